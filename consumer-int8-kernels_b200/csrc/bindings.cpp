@@ -1,0 +1,214 @@
+// torch stable-ABI operators of namespace consumer_int8 for the W8A8 linear path, as thin
+// wrappers over the C ABI in include/ci8.h. Schemas, argument checks and error texts follow the
+// reference's csrc/bindings.cpp (quantize_rows :191-209, quantize_grouped4096 :210-237,
+// channel_mm :238-265, channel_gemv :289-310, cutlass/fused_channel_mm :386-427, schemas
+// :593-613). Every output is caller-owned; nothing here allocates or synchronises.
+#include <Python.h>
+#include <torch/csrc/stable/library.h>
+#include <torch/csrc/stable/tensor.h>
+#include <torch/csrc/stable/accelerator.h>
+#include <torch/csrc/inductor/aoti_torch/c/shim.h>
+#include <torch/headeronly/util/Exception.h>
+#include <cstdint>
+#include <limits>
+#include "../../include/ci8.h"
+
+using torch::stable::Tensor;
+using torch::headeronly::ScalarType;
+using torch::stable::detail::to;
+
+namespace {
+constexpr int64_t kIntMax = std::numeric_limits<int>::max();
+
+void check(const Tensor& t, ScalarType dtype, int device) {
+  STD_TORCH_CHECK(t.is_cuda() && t.get_device_index() == device,
+                  "All tensors must be on the same CUDA device");
+  STD_TORCH_CHECK(t.is_contiguous() && t.scalar_type() == dtype,
+                  "Unexpected dtype or noncontiguous tensor");
+}
+ci8_stream_t stream_for(int device) {
+  void* stream = nullptr;
+  TORCH_ERROR_CODE_CHECK(aoti_torch_get_current_cuda_stream(device, &stream));
+  return reinterpret_cast<ci8_stream_t>(stream);
+}
+void launched(int code) { STD_TORCH_CHECK(code == 0, ci8_error_string(code)); }
+uintptr_t address(const Tensor& t) { return reinterpret_cast<uintptr_t>(t.data_ptr()); }
+
+void boxed_quant(StableIValue* stack, uint64_t, uint64_t) {
+  auto x = to<Tensor>(stack[0]), codes = to<Tensor>(stack[1]), scale = to<Tensor>(stack[2]);
+  const int device = x.get_device_index();
+  check(x, ScalarType::BFloat16, device);
+  check(codes, ScalarType::Char, device);
+  check(scale, ScalarType::Float, device);
+  STD_TORCH_CHECK(x.dim() == 2 && x.size(0) > 0 && x.size(1) > 0, "Expected a nonempty BF16 matrix");
+  STD_TORCH_CHECK(codes.dim() == 2 && codes.size(0) == x.size(0) && codes.size(1) == x.size(1) &&
+                      scale.dim() == 1 && scale.size(0) == x.size(0),
+                  "Wrong output shapes");
+  STD_TORCH_CHECK(x.numel() <= kIntMax, "Matrix too large");
+  torch::stable::accelerator::DeviceGuard guard(device);
+  launched(ci8_quantize_rows(x.data_ptr(), static_cast<int8_t*>(codes.data_ptr()),
+                             static_cast<float*>(scale.data_ptr()), x.size(0), x.size(1),
+                             stream_for(device)));
+}
+
+void boxed_grouped_quant(StableIValue* stack, uint64_t, uint64_t) {
+  auto x = to<Tensor>(stack[0]), codes = to<Tensor>(stack[1]), scales = to<Tensor>(stack[2]);
+  const int device = x.get_device_index();
+  check(x, ScalarType::BFloat16, device);
+  check(codes, ScalarType::Char, device);
+  check(scales, ScalarType::Float, device);
+  STD_TORCH_CHECK(x.dim() == 3 && x.size(1) > 0 && x.size(2) == 4096 && codes.dim() == 3 &&
+                      codes.size(0) == x.size(1) && codes.size(1) == x.size(0) && codes.size(2) == 4096 &&
+                      scales.dim() == 2 && scales.size(0) == x.size(1) && scales.size(1) == x.size(0) &&
+                      x.numel() <= kIntMax,
+                  "Expected BF16 input[M,G,4096], INT8 codes[G,M,4096], FP32 scales[G,M]");
+  STD_TORCH_CHECK(address(x) % 16 == 0 && address(codes) % 8 == 0 && address(scales) % 4 == 0,
+                  "Grouped quantization requires aligned buffers");
+  auto overlap = [](const Tensor& a, int64_t bytes_a, const Tensor& b, int64_t bytes_b) {
+    const uintptr_t first = address(a), second = address(b);
+    return a.numel() && b.numel() && first < second + b.numel() * bytes_b &&
+           second < first + a.numel() * bytes_a;
+  };
+  STD_TORCH_CHECK(!overlap(x, 2, codes, 1) && !overlap(x, 2, scales, 4) && !overlap(codes, 1, scales, 4),
+                  "Grouped quantization buffers must not overlap");
+  torch::stable::accelerator::DeviceGuard guard(device);
+  launched(ci8_quantize_grouped4096(x.data_ptr(), static_cast<int8_t*>(codes.data_ptr()),
+                                    static_cast<float*>(scales.data_ptr()), x.size(0), x.size(1),
+                                    stream_for(device)));
+}
+
+void boxed_mm(StableIValue* stack, uint64_t, uint64_t) {
+  auto a = to<Tensor>(stack[0]), w = to<Tensor>(stack[1]), sa = to<Tensor>(stack[2]);
+  auto sw = to<Tensor>(stack[3]), out = to<Tensor>(stack[4]);
+  const int device = a.get_device_index();
+  check(a, ScalarType::Char, device);
+  check(w, ScalarType::Byte, device);
+  check(sa, ScalarType::Float, device);
+  check(sw, ScalarType::BFloat16, device);
+  check(out, ScalarType::BFloat16, device);
+  STD_TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && out.dim() == 2, "Expected matrices");
+  const int64_t m = a.size(0), n = w.size(0), k = a.size(1);
+  STD_TORCH_CHECK(m > 0 && n > 0 && k > 0 && k % 32 == 0 && k <= 65536 && w.size(1) == k,
+                  "Invalid matrix geometry");
+  STD_TORCH_CHECK(sa.dim() == 1 && sa.size(0) == m && sw.dim() == 1 && sw.size(0) == n &&
+                      out.size(0) == m && out.size(1) == n,
+                  "Wrong scale or output shapes");
+  STD_TORCH_CHECK(a.numel() <= kIntMax && w.numel() <= kIntMax, "Matrix too large");
+  STD_TORCH_CHECK(address(a) % 16 == 0 && address(w) % 16 == 0, "Matrix operands must be 16-byte aligned");
+  torch::stable::accelerator::DeviceGuard guard(device);
+  launched(ci8_channel_mm(static_cast<int8_t*>(a.data_ptr()), static_cast<uint8_t*>(w.data_ptr()),
+                          static_cast<float*>(sa.data_ptr()), sw.data_ptr(), out.data_ptr(), m, n, k,
+                          stream_for(device)));
+}
+
+void boxed_gemv(StableIValue* stack, uint64_t, uint64_t) {
+  auto x = to<Tensor>(stack[0]), w = to<Tensor>(stack[1]);
+  auto scale = to<Tensor>(stack[2]), out = to<Tensor>(stack[3]);
+  const int device = x.get_device_index();
+  check(x, ScalarType::BFloat16, device);
+  check(w, ScalarType::Char, device);
+  check(scale, ScalarType::BFloat16, device);
+  check(out, ScalarType::BFloat16, device);
+  STD_TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2 && scale.dim() == 1,
+                  "Expected input/weight/output matrices and channel scales");
+  const int64_t m = x.size(0), n = w.size(0), k = x.size(1);
+  // The reference stops at 8 rows; this build accepts up to 16 (a superset).
+  STD_TORCH_CHECK(m > 0 && m <= 16 && n > 0 && k > 0 && k <= 65536 && k % 16 == 0 && w.size(1) == k &&
+                      scale.size(0) == n && out.size(0) == m && out.size(1) == n,
+                  "Unsupported W8A16 GEMV geometry");
+  STD_TORCH_CHECK(w.numel() <= kIntMax, "Weight matrix too large");
+  STD_TORCH_CHECK(address(w) % 16 == 0 && address(x) % 4 == 0, "Unaligned vector inputs");
+  torch::stable::accelerator::DeviceGuard guard(device);
+  launched(ci8_channel_gemv(x.data_ptr(), static_cast<int8_t*>(w.data_ptr()), scale.data_ptr(),
+                            out.data_ptr(), m, n, k, stream_for(device)));
+}
+
+void tiled_mm_impl(StableIValue* stack, bool fused) {
+  auto a = to<Tensor>(stack[0]), w = to<Tensor>(stack[1]);
+  auto sa = to<Tensor>(stack[2]), sw = to<Tensor>(stack[3]);
+  auto out = to<Tensor>(stack[fused ? 4 : 5]);
+  const int device = a.get_device_index();
+  check(a, ScalarType::Char, device);
+  check(w, ScalarType::Char, device);
+  check(sa, ScalarType::Float, device);
+  check(sw, ScalarType::BFloat16, device);
+  check(out, ScalarType::BFloat16, device);
+  STD_TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && out.dim() == 2, "Expected matrices");
+  const int64_t m = a.size(0), n = w.size(0), k = a.size(1);
+  STD_TORCH_CHECK(m > 0 && n > 0 && k > 0 && n % 4 == 0 && k % 32 == 0 && k <= 65536 && w.size(1) == k &&
+                      out.size(0) == m && out.size(1) == n && sa.dim() == 1 && sw.dim() == 1 &&
+                      sa.size(0) == m && sw.size(0) == n,
+                  "Invalid CUTLASS geometry");
+  STD_TORCH_CHECK(a.numel() <= kIntMax && w.numel() <= kIntMax && out.numel() <= kIntMax, "Matrix too large");
+  STD_TORCH_CHECK(address(a) % 16 == 0 && address(w) % 16 == 0, "Matrix operands must be 16-byte aligned");
+  torch::stable::accelerator::DeviceGuard guard(device);
+  if (fused) {
+    const int64_t schedule = to<int64_t>(stack[5]);
+    STD_TORCH_CHECK(schedule >= 0 && schedule <= 6, "Invalid fused GEMM schedule");
+    launched(ci8_fused_channel_mm(static_cast<int8_t*>(a.data_ptr()), static_cast<int8_t*>(w.data_ptr()),
+                                  static_cast<float*>(sa.data_ptr()), sw.data_ptr(), out.data_ptr(), m, n, k,
+                                  static_cast<int>(schedule), stream_for(device)));
+  } else {
+    auto workspace = to<Tensor>(stack[4]);
+    check(workspace, ScalarType::Int, device);
+    STD_TORCH_CHECK(workspace.dim() == 2 && workspace.size(0) == m && workspace.size(1) == n,
+                    "Expected matching workspace");
+    launched(ci8_cutlass_channel_mm(static_cast<int8_t*>(a.data_ptr()), static_cast<int8_t*>(w.data_ptr()),
+                                    static_cast<float*>(sa.data_ptr()), sw.data_ptr(),
+                                    static_cast<int32_t*>(workspace.data_ptr()), out.data_ptr(), m, n, k,
+                                    stream_for(device)));
+  }
+}
+void boxed_cutlass_mm(StableIValue* stack, uint64_t, uint64_t) { tiled_mm_impl(stack, false); }
+void boxed_fused_mm(StableIValue* stack, uint64_t, uint64_t) { tiled_mm_impl(stack, true); }
+
+// Additive operator (no counterpart in the reference's surface): the grouped-scale GEMM in one
+// launch, consuming what quantize_grouped4096 writes.
+void boxed_grouped_mm(StableIValue* stack, uint64_t, uint64_t) {
+  auto codes = to<Tensor>(stack[0]), w = to<Tensor>(stack[1]), scales = to<Tensor>(stack[2]);
+  auto sw = to<Tensor>(stack[3]), out = to<Tensor>(stack[4]);
+  const int device = codes.get_device_index();
+  check(codes, ScalarType::Char, device);
+  check(w, ScalarType::Char, device);
+  check(scales, ScalarType::Float, device);
+  check(sw, ScalarType::BFloat16, device);
+  check(out, ScalarType::BFloat16, device);
+  STD_TORCH_CHECK(codes.dim() == 3 && codes.size(2) == 4096 && w.dim() == 2 && scales.dim() == 2 &&
+                      sw.dim() == 1 && out.dim() == 2,
+                  "Expected INT8 codes[G,M,4096], INT8 w[N,G*4096], FP32 scales[G,M], BF16 w_scale[N], BF16 out[M,N]");
+  const int64_t groups = codes.size(0), m = codes.size(1), n = w.size(0);
+  STD_TORCH_CHECK(groups > 0 && groups <= 16 && m > 0 && n > 0 && w.size(1) == groups * 4096 &&
+                      scales.size(0) == groups && scales.size(1) == m && sw.size(0) == n &&
+                      out.size(0) == m && out.size(1) == n,
+                  "Invalid grouped GEMM geometry");
+  STD_TORCH_CHECK(codes.numel() <= kIntMax && w.numel() <= kIntMax && out.numel() <= kIntMax, "Matrix too large");
+  STD_TORCH_CHECK(address(codes) % 16 == 0 && address(w) % 16 == 0, "Matrix operands must be 16-byte aligned");
+  torch::stable::accelerator::DeviceGuard guard(device);
+  launched(ci8_grouped_channel_mm(static_cast<int8_t*>(codes.data_ptr()), static_cast<int8_t*>(w.data_ptr()),
+                                  static_cast<float*>(scales.data_ptr()), sw.data_ptr(), out.data_ptr(), m, n,
+                                  groups, stream_for(device)));
+}
+}  // namespace
+
+STABLE_TORCH_LIBRARY(consumer_int8, m) {
+  m.def("fused_channel_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) out, int schedule=0) -> ()");
+  m.def("quantize_rows(Tensor input, Tensor(a!) codes, Tensor(b!) scales) -> ()");
+  m.def("quantize_grouped4096(Tensor input, Tensor(a!) codes, Tensor(b!) scales) -> ()");
+  m.def("channel_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) out) -> ()");
+  m.def("channel_gemv(Tensor x, Tensor w, Tensor scale, Tensor(a!) out) -> ()");
+  m.def("cutlass_channel_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) workspace, Tensor(b!) out) -> ()");
+  m.def("grouped_channel_mm(Tensor codes, Tensor w, Tensor scales, Tensor w_scale, Tensor(a!) out) -> ()");
+}
+STABLE_TORCH_LIBRARY_IMPL(consumer_int8, CUDA, m) {
+  m.impl("fused_channel_mm", &boxed_fused_mm);
+  m.impl("quantize_rows", &boxed_quant);
+  m.impl("quantize_grouped4096", &boxed_grouped_quant);
+  m.impl("channel_mm", &boxed_mm);
+  m.impl("channel_gemv", &boxed_gemv);
+  m.impl("cutlass_channel_mm", &boxed_cutlass_mm);
+  m.impl("grouped_channel_mm", &boxed_grouped_mm);
+}
+extern "C" PyObject* PyInit__C() {
+  static PyModuleDef module = {PyModuleDef_HEAD_INIT, "_C", nullptr, -1, nullptr};
+  return PyModule_Create(&module);
+}

@@ -1,0 +1,392 @@
+// Host side of libci8.so: argument checks, tensor-map construction, schedule selection and
+// launches behind the C ABI declared in include/ci8.h. No allocation, no synchronisation.
+#include "../../include/ci8.h"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+
+#include "decode_splitk.cuh"
+#include "gemm_tcgen05.cuh"
+#include "gemv_w8a16.cuh"
+#include "quantize.cuh"
+
+namespace {
+
+using namespace ci8;
+
+constexpr int kInvalid = static_cast<int>(cudaErrorInvalidValue);
+constexpr int kMaxDevices = 64;
+
+// ------------------------------------------------------------------ per-device facts
+struct DeviceInfo {
+  std::atomic<int> sm_count{0};
+};
+DeviceInfo g_devices[kMaxDevices];
+
+int sm_count() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return 148;
+  int count = g_devices[device].sm_count.load(std::memory_order_relaxed);
+  if (count == 0) {
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+      count = 148;
+    g_devices[device].sm_count.store(count, std::memory_order_relaxed);
+  }
+  return count;
+}
+
+// Raises a kernel's dynamic shared-memory limit once per device (idempotent, capture-safe).
+template <typename Kernel>
+cudaError_t ensure_smem(Kernel kernel, int bytes, std::atomic<uint64_t>& done_mask) {
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return err;
+  const uint64_t bit = uint64_t(1) << (device & 63);
+  if (done_mask.load(std::memory_order_acquire) & bit) return cudaSuccess;
+  err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (err == cudaSuccess) done_mask.fetch_or(bit, std::memory_order_release);
+  return err;
+}
+
+// ------------------------------------------------------------------ tensor maps
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled_fn() {
+  static std::atomic<void*> cached{nullptr};
+  void* fn = cached.load(std::memory_order_acquire);
+  if (!fn) {
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query) != cudaSuccess ||
+        query != cudaDriverEntryPointSuccess)
+      return nullptr;
+    cached.store(fn, std::memory_order_release);
+  }
+  return reinterpret_cast<EncodeTiled>(fn);
+}
+
+// Row-major byte matrix [rows, cols] -> tiles of box_rows x 128 bytes, 128-byte swizzle,
+// out-of-range elements read as zero.
+cudaError_t make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiled encode = encode_tiled_fn();
+  if (!encode) return cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols};
+  const cuuint32_t box[2] = {128u, box_rows};
+  const cuuint32_t elem[2] = {1u, 1u};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+                            box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+bool aligned(const void* p, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(p) % bytes == 0; }
+
+// ------------------------------------------------------------------ tcgen05 GEMM launch
+template <int kCtas, int kMode>
+cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cudaStream_t stream) {
+  using Cfg = GemmConfig<kCtas, kMode>;
+  static std::atomic<uint64_t> smem_done{0};
+  auto kernel = gemm_i8_kernel<kCtas, kMode>;
+  cudaError_t err = ensure_smem(kernel, Cfg::kSmemBytes, smem_done);
+  if (err != cudaSuccess) return err;
+
+  GemmParams p = base;
+  p.tiles_m = (p.m + Cfg::kBlockM * kCtas - 1) / (Cfg::kBlockM * kCtas);
+  p.tiles_n = (p.n + Cfg::kChannelsPerTile - 1) / Cfg::kChannelsPerTile;
+  CUtensorMap map_a, map_w;
+  err = make_map(&map_a, a, static_cast<uint64_t>(p.m) * p.groups, p.k, Cfg::kBlockM);
+  if (err != cudaSuccess) return err;
+  err = make_map(&map_w, w, p.n, static_cast<uint64_t>(p.k) * p.groups, Cfg::kBRowsLoad);
+  if (err != cudaSuccess) return err;
+
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const int sms = sm_count();
+  cudaLaunchConfig_t config = {};
+  cudaLaunchAttribute attr[1];
+  if (kCtas == 2) {
+    const long long clusters = tiles < sms / 2 ? tiles : sms / 2;
+    config.gridDim = dim3(static_cast<unsigned>(2 * clusters));
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+  } else {
+    config.gridDim = dim3(static_cast<unsigned>(tiles < sms ? tiles : sms));
+  }
+  config.blockDim = dim3(Cfg::kThreads);
+  config.dynamicSmemBytes = Cfg::kSmemBytes;
+  config.stream = stream;
+  return cudaLaunchKernelEx(&config, kernel, map_a, map_w, p);
+}
+
+// ------------------------------------------------------------------ decode (M <= 16) launch
+// Picks the split-K factor and the slab width (channels per CTA) that minimise the bytes the
+// busiest SM has to stream: waves * slab * K / split.
+void choose_decode_shape(int n, int k, int sms, int* split_out, int* slab_out) {
+  const int num_kb = (k + 127) / 128;
+  double best = 1e300;
+  int best_split = 1, best_slab = 128;
+  for (int split = 1; split <= 4; split *= 2) {
+    if (split > num_kb) break;
+    for (int slab = 128; slab <= 256; slab += 16) {
+      const long long slabs = (n + slab - 1) / slab;
+      const long long ctas = slabs * split;
+      const long long waves = (ctas + sms - 1) / sms;
+      // a small per-CTA constant keeps needless splits from winning ties
+      const double cost = static_cast<double>(waves) * (static_cast<double>(slab) * ((num_kb + split - 1) / split) + 64.0 * split);
+      if (cost < best) { best = cost; best_split = split; best_slab = slab; }
+    }
+  }
+  *split_out = best_split;
+  *slab_out = best_slab;
+}
+
+template <int kSplit, bool kBiased>
+cudaError_t launch_decode_variant(const void* a, const void* w, const DecodeParams& p, cudaStream_t stream) {
+  using Cfg = DecodeConfig<kSplit>;
+  static std::atomic<uint64_t> smem_done{0};
+  auto kernel = decode_w8a8_kernel<kSplit, kBiased>;
+  cudaError_t err = ensure_smem(kernel, Cfg::kSmemBytes, smem_done);
+  if (err != cudaSuccess) return err;
+  CUtensorMap map_w, map_a;
+  err = make_map(&map_w, w, p.n, p.k, p.slab);
+  if (err != cudaSuccess) return err;
+  err = make_map(&map_a, a, p.m, p.k, Cfg::kRows);
+  if (err != cudaSuccess) return err;
+  const int slabs = (p.n + p.slab - 1) / p.slab;
+  cudaLaunchConfig_t config = {};
+  cudaLaunchAttribute attr[1];
+  config.gridDim = dim3(static_cast<unsigned>(slabs * kSplit));
+  config.blockDim = dim3(Cfg::kThreads);
+  config.dynamicSmemBytes = Cfg::kSmemBytes;
+  config.stream = stream;
+  if (kSplit > 1) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kSplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&config, kernel, map_w, map_a, p);
+}
+
+template <bool kBiased>
+cudaError_t launch_decode(const void* a, const void* w, DecodeParams p, int forced_split, cudaStream_t stream) {
+  int split = 1, slab = 128;
+  choose_decode_shape(p.n, p.k, sm_count(), &split, &slab);
+  if (forced_split > 0) {
+    split = forced_split;
+    const int per = sm_count() / split > 0 ? sm_count() / split : 1;
+    slab = ((p.n + per - 1) / per + 15) / 16 * 16;
+    if (slab < 128) slab = 128;
+    if (slab > 256) slab = 256;
+  }
+  p.slab = slab;
+  switch (split) {
+    case 1: return launch_decode_variant<1, kBiased>(a, w, p, stream);
+    case 2: return launch_decode_variant<2, kBiased>(a, w, p, stream);
+    default: return launch_decode_variant<4, kBiased>(a, w, p, stream);
+  }
+}
+
+bool gemm_geometry_ok(int m, int n, int k) {
+  return m > 0 && n > 0 && k > 0 && k % 32 == 0 && k <= 65536 &&
+         static_cast<long long>(m) * k <= INT32_MAX && static_cast<long long>(n) * k <= INT32_MAX;
+}
+
+// ------------------------------------------------------------------ quantizer launch
+template <int kTeam, int kPacks>
+void launch_quantize_vec(const void* x, int8_t* q, float* s, int rows, int k, int m, int groups, cudaStream_t stream) {
+  constexpr int kRowsPerCta = 256 / kTeam;
+  quantize_rows_vec_kernel<kTeam, kPacks><<<(rows + kRowsPerCta - 1) / kRowsPerCta, 256, 0, stream>>>(
+      static_cast<const uint16_t*>(x), q, s, rows, k, m, groups);
+}
+
+// rows = output rows; groups == 0 for the plain form.
+cudaError_t launch_quantize(const void* x, int8_t* q, float* s, int rows, int k, int m, int groups,
+                            cudaStream_t stream) {
+  const bool vector_ok = k % 8 == 0 && aligned(x, 16) && aligned(q, 8);
+  const int packs = k / 8;
+  if (vector_ok && packs <= 32 * 32 && rows >= 64) {
+    // one warp per row: up to 32 packs per lane
+    const int per_lane = (packs + 31) / 32;
+#define CI8_WARP(P) launch_quantize_vec<32, P>(x, q, s, rows, k, m, groups, stream)
+    if (per_lane <= 4) CI8_WARP(4);
+    else if (per_lane <= 8) CI8_WARP(8);
+    else if (per_lane <= 12) CI8_WARP(12);
+    else if (per_lane <= 16) CI8_WARP(16);
+    else if (per_lane <= 20) CI8_WARP(20);
+    else if (per_lane <= 24) CI8_WARP(24);
+    else CI8_WARP(32);
+#undef CI8_WARP
+  } else if (vector_ok && packs <= 256 * 32) {
+    // one 256-thread CTA per row
+    const int per_thread = (packs + 255) / 256;
+#define CI8_CTA(P) launch_quantize_vec<256, P>(x, q, s, rows, k, m, groups, stream)
+    if (per_thread <= 1) CI8_CTA(1);
+    else if (per_thread <= 2) CI8_CTA(2);
+    else if (per_thread <= 3) CI8_CTA(3);
+    else if (per_thread <= 4) CI8_CTA(4);
+    else if (per_thread <= 6) CI8_CTA(6);
+    else if (per_thread <= 9) CI8_CTA(9);
+    else if (per_thread <= 12) CI8_CTA(12);
+    else if (per_thread <= 16) CI8_CTA(16);
+    else if (per_thread <= 24) CI8_CTA(24);
+    else CI8_CTA(32);
+#undef CI8_CTA
+  } else {
+    if (groups > 0) return cudaErrorInvalidValue;   // the grouped form requires aligned buffers
+    quantize_rows_generic_kernel<<<rows, 256, 0, stream>>>(static_cast<const uint16_t*>(x), q, s, k);
+  }
+  return cudaGetLastError();
+}
+
+template <int kRows>
+cudaError_t launch_gemv(const void* x, const int8_t* w, const void* sw, void* out, int m, int n, int k,
+                        cudaStream_t stream) {
+  constexpr int kChannels = kRows <= 4 ? 4 : 2;
+  constexpr int kSmem = kRows * kGemvChunk * 2;
+  static std::atomic<uint64_t> smem_done{0};
+  auto kernel = gemv_w8a16_kernel<kRows, kChannels>;
+  cudaError_t err = ensure_smem(kernel, kSmem, smem_done);
+  if (err != cudaSuccess) return err;
+  const int per_cta = 8 * kChannels;
+  kernel<<<(n + per_cta - 1) / per_cta, 256, kSmem, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), w, static_cast<const __nv_bfloat16*>(sw),
+      static_cast<__nv_bfloat16*>(out), m, n, k);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// ====================================================================== C ABI
+extern "C" {
+
+int ci8_abi_version(void) { return 1; }
+
+const char* ci8_error_string(int code) {
+  return code == 0 ? "success" : cudaGetErrorString(static_cast<cudaError_t>(code));
+}
+
+int ci8_device_status(unsigned* status) {
+  if (!status) return kInvalid;
+  cudaError_t err = cudaDeviceSynchronize();
+  if (err != cudaSuccess) return err;
+  err = cudaMemcpyFromSymbol(status, ci8::g_ci8_status, sizeof(unsigned));
+  if (err != cudaSuccess) return err;
+  const unsigned zero = 0;
+  return cudaMemcpyToSymbol(ci8::g_ci8_status, &zero, sizeof(unsigned));
+}
+
+int ci8_quantize_rows(const void* x, int8_t* codes, float* scales, int m, int k, ci8_stream_t stream) {
+  if (!x || !codes || !scales || m <= 0 || k <= 0 || static_cast<long long>(m) * k > INT32_MAX) return kInvalid;
+  return launch_quantize(x, codes, scales, m, k, m, 0, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ci8_quantize_grouped4096(const void* x, int8_t* codes, float* scales, int m, int groups,
+                             ci8_stream_t stream) {
+  if (m < 0 || groups <= 0 || static_cast<long long>(m) * groups * 4096 > INT32_MAX) return kInvalid;
+  if (m == 0) return 0;
+  if (!x || !codes || !scales || !aligned(x, 16) || !aligned(codes, 8) || !aligned(scales, 4)) return kInvalid;
+  return launch_quantize(x, codes, scales, m * groups, 4096, m, groups, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ci8_fused_channel_mm(const int8_t* a, const int8_t* w, const float* a_scale, const void* w_scale,
+                         void* out, int m, int n, int k, int schedule, ci8_stream_t stream) {
+  if (!a || !w || !a_scale || !w_scale || !out || !gemm_geometry_ok(m, n, k) || schedule < 0 || schedule > 6 ||
+      !aligned(a, 16) || !aligned(w, 16) || static_cast<long long>(m) * n > INT32_MAX)
+    return kInvalid;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (m <= 16 && schedule == 0) {
+    DecodeParams p{a, a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out),
+                   nullptr, m, n, k, 0};
+    return launch_decode<false>(a, w, p, 0, s);
+  }
+  GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
+               m, n, k, 1, 0, 0};
+  // schedule 0: pairs of CTAs once there is more than one 128-row block; odd values force the
+  // single-CTA tile, even values the two-CTA tile. All give identical bits.
+  const bool pair = schedule == 0 ? m > 128 : (schedule % 2 == 0);
+  return pair ? launch_gemm<2, kModeFused>(a, w, p, s) : launch_gemm<1, kModeFused>(a, w, p, s);
+}
+
+int ci8_cutlass_channel_mm(const int8_t* a, const int8_t* w, const float* a_scale, const void* w_scale,
+                           int32_t* workspace, void* out, int m, int n, int k, ci8_stream_t stream) {
+  if (!a || !w || !a_scale || !w_scale || !workspace || !out || !gemm_geometry_ok(m, n, k) || !aligned(a, 16) ||
+      !aligned(w, 16) || static_cast<long long>(m) * n > INT32_MAX)
+    return kInvalid;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (m <= 16) {
+    DecodeParams p{a, a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out),
+                   workspace, m, n, k, 0};
+    return launch_decode<false>(a, w, p, 0, s);
+  }
+  GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), workspace,
+               m, n, k, 1, 0, 0};
+  return m > 128 ? launch_gemm<2, kModeWorkspace>(a, w, p, s) : launch_gemm<1, kModeWorkspace>(a, w, p, s);
+}
+
+int ci8_channel_mm(const int8_t* a, const uint8_t* w, const float* a_scale, const void* w_scale, void* out,
+                   int m, int n, int k, ci8_stream_t stream) {
+  if (!a || !w || !a_scale || !w_scale || !out || !gemm_geometry_ok(m, n, k) || !aligned(a, 16) || !aligned(w, 16))
+    return kInvalid;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (m <= 16) {
+    DecodeParams p{a, a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out),
+                   nullptr, m, n, k, 0};
+    return launch_decode<true>(a, w, p, 0, s);
+  }
+  GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
+               m, n, k, 1, 0, 0};
+  return launch_gemm<1, kModeBiased>(a, w, p, s);
+}
+
+int ci8_channel_gemv(const void* x, const int8_t* w, const void* w_scale, void* out, int m, int n, int k,
+                     ci8_stream_t stream) {
+  if (!x || !w || !w_scale || !out || m <= 0 || m > 16 || n <= 0 || k <= 0 || k > 65536 || k % 16 != 0 ||
+      static_cast<long long>(n) * k > INT32_MAX || !aligned(w, 16) || !aligned(x, 4))
+    return kInvalid;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (m == 1) return launch_gemv<1>(x, w, w_scale, out, m, n, k, s);
+  if (m == 2) return launch_gemv<2>(x, w, w_scale, out, m, n, k, s);
+  if (m <= 4) return launch_gemv<4>(x, w, w_scale, out, m, n, k, s);
+  if (m <= 8) return launch_gemv<8>(x, w, w_scale, out, m, n, k, s);
+  return launch_gemv<16>(x, w, w_scale, out, m, n, k, s);
+}
+
+int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* scales, const void* w_scale,
+                           void* out, int m, int n, int groups, ci8_stream_t stream) {
+  if (!codes || !w || !scales || !w_scale || !out || m <= 0 || n <= 0 || groups <= 0 || groups > 16 ||
+      static_cast<long long>(m) * groups * 4096 > INT32_MAX || static_cast<long long>(n) * groups * 4096 > INT32_MAX ||
+      static_cast<long long>(m) * n > INT32_MAX || !aligned(codes, 16) || !aligned(w, 16))
+    return kInvalid;
+  GemmParams p{scales, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
+               m, n, 4096, groups, 0, 0};
+  return launch_gemm<1, kModeGrouped>(codes, w, p, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Test hook: the decode kernel with a forced split-K factor (1, 2 or 4); weights_biased != 0
+// selects the UINT8 form. Same contract as ci8_fused_channel_mm / ci8_channel_mm with m <= 16.
+int ci8_decode_mm_split(const int8_t* a, const void* w, const float* a_scale, const void* w_scale,
+                        int32_t* workspace, void* out, int m, int n, int k, int split, int weights_biased,
+                        ci8_stream_t stream) {
+  if (!a || !w || !a_scale || !w_scale || !out || !gemm_geometry_ok(m, n, k) || m > 16 ||
+      (split != 1 && split != 2 && split != 4) || split > (k + 127) / 128 || !aligned(a, 16) || !aligned(w, 16))
+    return kInvalid;
+  DecodeParams p{a, a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out),
+                 workspace, m, n, k, 0};
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return weights_biased ? launch_decode<true>(a, w, p, split, s) : launch_decode<false>(a, w, p, split, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,339 @@
+// Persistent, warp-specialised INT8 GEMM for sm_100a:  acc[m,n] = sum_k a[m,k] * w[n,k]  (INT32),
+// out = bf16((float(acc) * sa[m]) * float(sw[n])).
+//
+//   warp 0      TMA producer: 128-byte-swizzled K-major tiles of A [M,K] and W [N,K] into a
+//               shared-memory ring (one elected lane)
+//   warp 1      tcgen05.mma kind::i8 issuer (one elected lane), accumulators in TMEM,
+//               two 256-column accumulator buffers so a tile's epilogue overlaps the next
+//               tile's main loop; also owns the TMEM allocation
+//   warps 2..   epilogue: tcgen05.ld -> FP32 row scale -> FP32 channel scale -> BF16 stores
+//
+// kCtas == 1: one CTA per 128x256 output tile.
+// kCtas == 2: a two-CTA cluster shares a 256x256 tile; each CTA stages its own 128 rows of A
+//             and its own 128 rows of W (plain, non-multicast TMA loads) and the pair leader
+//             issues tcgen05.mma.cta_group::2, which reads both CTAs' shared memory.
+// Modes:
+//   kModeFused      signed INT8 weights, BF16 output only (fused_channel_mm)
+//   kModeWorkspace  as fused, and the INT32 accumulators are also written to a caller buffer
+//                   (cutlass_channel_mm)
+//   kModeBiased     UINT8 weights holding code+128 (channel_mm): the weight tile carries 240
+//                   channels plus 16 rows of ones, so accumulator column 240 is sum_k a[m,k]
+//                   and the signed product is acc - 128 * that sum, still exact INT32
+//   kModeGrouped    K is G groups of 4096 with one activation scale per (group,row): each
+//                   group's INT32 accumulator is converted, scaled and added in FP32 in
+//                   ascending group order (separate multiply and add), then the channel
+//                   scale is applied (grouped_channel_mm)
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include "sm100_ptx.cuh"
+
+namespace ci8 {
+
+enum GemmMode { kModeFused = 0, kModeWorkspace = 1, kModeBiased = 2, kModeGrouped = 3 };
+
+struct GemmParams {
+  const float* sa;            // [M] (grouped: [G,M])
+  const __nv_bfloat16* sw;    // [N]
+  __nv_bfloat16* out;         // [M,N]
+  int32_t* workspace;         // [M,N] or nullptr
+  int m, n, k;                // k = K per group
+  int groups;                 // 1 unless grouped
+  int tiles_m, tiles_n;
+};
+
+template <int kCtas, int kMode>
+struct GemmConfig {
+  static constexpr int kBlockM = 128;                 // rows of A per CTA
+  static constexpr int kTileN = 256;                  // accumulator columns per tile
+  static constexpr int kBlockK = 128;                 // bytes of K per stage
+  static constexpr int kOnesRows = kMode == kModeBiased ? 16 : 0;
+  static constexpr int kChannelsPerTile = kTileN - kOnesRows;   // output channels per tile
+  static constexpr int kBRowsSmem = kTileN / kCtas;   // weight rows held by one CTA
+  static constexpr int kBRowsLoad = kBRowsSmem - (kCtas == 1 ? kOnesRows : 0);
+  static constexpr int kABytes = kBlockM * kBlockK;
+  static constexpr int kBBytes = kBRowsSmem * kBlockK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStageTx = kABytes + kBRowsLoad * kBlockK;
+  static constexpr int kStages = kCtas == 1 ? 4 : 6;
+  static constexpr int kEpiWarps = kMode == kModeGrouped ? 8 : 4;
+  static constexpr int kThreads = (2 + kEpiWarps) * 32;
+  static constexpr int kColsPerEpiWarp = kTileN / (kEpiWarps / 4);
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + align slack
+  static_assert(kMode != kModeBiased || kCtas == 1, "biased weights use the single-CTA tile");
+};
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int kCtas, int kMode>
+__global__ void __launch_bounds__(GemmConfig<kCtas, kMode>::kThreads, 1)
+gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
+               const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+  using Cfg = GemmConfig<kCtas, kMode>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+  uint8_t* bar_region = smem + Cfg::kStages * Cfg::kStageBytes;
+  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  // barrier layout (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
+  auto tmem_full_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + b); };
+  auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + 2 + b); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_region + 8 * (2 * Cfg::kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = kCtas == 2 ? cluster_ctarank() : 0u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tmem_full_bar(b), 1);
+      mbar_init(tmem_empty_bar(b), Cfg::kEpiWarps * kCtas);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_w);
+  }
+  if constexpr (kMode == kModeBiased) {
+    // Sixteen rows of ones behind the 240 weight rows of every stage (the swizzle permutes
+    // 16-byte chunks within a row, so a constant fill is layout-independent).
+    constexpr int kOnesBytes = Cfg::kOnesRows * Cfg::kBlockK;
+    for (int i = threadIdx.x; i < Cfg::kStages * (kOnesBytes / 16); i += Cfg::kThreads) {
+      const int s = i / (kOnesBytes / 16), c = i % (kOnesBytes / 16);
+      uint8_t* dst = smem + s * Cfg::kStageBytes + Cfg::kABytes + Cfg::kBRowsLoad * Cfg::kBlockK;
+      reinterpret_cast<uint4*>(dst)[c] = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
+    }
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) {
+    tmem_alloc<kCtas>(smem_u32(tmem_slot), 512);
+    tmem_relinquish<kCtas>();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if constexpr (kCtas == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;   // per group
+  const int total_tiles = p.tiles_m * p.tiles_n;
+  const int first_tile = kCtas == 2 ? (blockIdx.x >> 1) : blockIdx.x;
+  const int tile_stride = kCtas == 2 ? (gridDim.x >> 1) : gridDim.x;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t leader_full0 = kCtas == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
+      bool ok = true;
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
+        const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
+        const int a_row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM;
+        const int w_row = nt * Cfg::kChannelsPerTile + rank * Cfg::kBRowsSmem;
+        for (int g = 0; ok && g < p.groups; ++g) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+            if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageTx * kCtas);
+            const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
+            const uint32_t b_dst = a_dst + Cfg::kABytes;
+            const uint32_t bar = leader_full0 + 8u * stage;
+            const int kx = kb * Cfg::kBlockK;
+            if constexpr (kCtas == 2) {
+              tma_load_2d_pair(a_dst, &map_a, kx, g * p.m + a_row, bar);
+              tma_load_2d_pair(b_dst, &map_w, g * p.k + kx, w_row, bar);
+            } else {
+              tma_load_2d(a_dst, &map_a, kx, g * p.m + a_row, bar);
+              tma_load_2d(b_dst, &map_w, g * p.k + kx, w_row, bar);
+            }
+            if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+      if (!ok) __nanosleep(200000);  // let loads already in flight land before teardown
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (rank == 0 && lane == 0) {
+      constexpr uint32_t kIdesc =
+          idesc_i8(Cfg::kBlockM * kCtas, Cfg::kTileN, /*b_unsigned=*/kMode == kModeBiased);
+      int stage = 0;
+      uint32_t phase = 0, acc_iter = 0;
+      bool ok = true;
+      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
+        for (int g = 0; ok && g < p.groups; ++g, ++acc_iter) {
+          const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
+          if (!mbar_wait<kCtas == 2>(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t tmem_d = tmem_base + buf * Cfg::kTileN;
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait<kCtas == 2>(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+            tcgen05_fence_after();
+            const uint32_t a_addr = smem_base + stage * Cfg::kStageBytes;
+            const uint64_t a_desc = smem_desc_sw128(a_addr);
+            const uint64_t b_desc = smem_desc_sw128(a_addr + Cfg::kABytes);
+#pragma unroll
+            for (int ks = 0; ks < Cfg::kBlockK / 32; ++ks)
+              mma_i8<kCtas>(tmem_d, a_desc + 2u * ks, b_desc + 2u * ks, kIdesc,
+                            (kb | ks) != 0 ? 1u : 0u);
+            if constexpr (kCtas == 2) {
+              mma_commit_pair(map_to_cta(empty_bar(stage), 0));
+              mma_commit_pair(map_to_cta(empty_bar(stage), 1));
+            } else {
+              mma_commit(empty_bar(stage));
+            }
+            if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+          }
+          if (!ok) break;
+          if constexpr (kCtas == 2) {
+            mma_commit_pair(map_to_cta(tmem_full_bar(buf), 0));
+            mma_commit_pair(map_to_cta(tmem_full_bar(buf), 1));
+          } else {
+            mma_commit(tmem_full_bar(buf));
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int epi = warp - 2;
+    const int quarter = warp & 3;                       // TMEM lanes this warp may read
+    const int col_base = (epi >> 2) * Cfg::kColsPerEpiWarp;
+    constexpr int kChunks = Cfg::kColsPerEpiWarp / 32;
+    const uint32_t leader_empty0 = kCtas == 2 ? map_to_cta(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+    const bool out_vec = (p.n % 8 == 0) && (reinterpret_cast<uintptr_t>(p.out) % 16 == 0);
+    const bool ws_vec = (p.n % 4 == 0) && (reinterpret_cast<uintptr_t>(p.workspace) % 16 == 0);
+    uint32_t acc_iter = 0;
+    bool ok = true;
+    float total[kMode == kModeGrouped ? Cfg::kColsPerEpiWarp : 1];
+    for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
+      const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
+      const int row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM + quarter * 32 + lane;
+      const int n0 = nt * Cfg::kChannelsPerTile;
+      for (int g = 0; g < p.groups; ++g, ++acc_iter) {
+        const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
+        if (!mbar_wait<kCtas == 2>(tmem_full_bar(buf), acc_phase, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                               buf * Cfg::kTileN + col_base;
+        const float row_scale = row < p.m ? p.sa[static_cast<size_t>(g) * p.m + row] : 0.f;
+        int32_t bias = 0;
+        if constexpr (kMode == kModeBiased) {
+          uint32_t ones[16];
+          tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                            buf * Cfg::kTileN + Cfg::kChannelsPerTile, ones);
+          tmem_ld_wait();
+          bias = static_cast<int32_t>(ones[0]) * 128;
+        }
+#pragma unroll
+        for (int chunk = 0; chunk < kChunks; ++chunk) {
+          const int c0 = n0 + col_base + chunk * 32;
+          if (kMode == kModeBiased && col_base + chunk * 32 >= Cfg::kChannelsPerTile) break;
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + chunk * 32, v);
+          tmem_ld_wait();
+          if constexpr (kMode == kModeGrouped) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float term = __fmul_rn(__int2float_rn(static_cast<int32_t>(v[j])), row_scale);
+              total[chunk * 32 + j] = g == 0 ? term : __fadd_rn(total[chunk * 32 + j], term);
+            }
+            if (g + 1 < p.groups) continue;
+          }
+          if (c0 >= p.n) continue;
+          // channel scales for this chunk: lane j holds sw[c0 + j]
+          const float my_sw = (c0 + lane < p.n) ? __bfloat162float(p.sw[c0 + lane]) : 0.f;
+          const int limit = kMode == kModeBiased
+                                ? min(p.n - c0, Cfg::kChannelsPerTile - (col_base + chunk * 32))
+                                : p.n - c0;
+          if constexpr (kMode == kModeBiased || kMode == kModeWorkspace) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = static_cast<uint32_t>(static_cast<int32_t>(v[j]) - bias);
+          }
+          if constexpr (kMode == kModeWorkspace) {
+            if (row < p.m) {
+              int32_t* ws = p.workspace + static_cast<size_t>(row) * p.n + c0;
+              if (ws_vec && limit >= 32) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<uint4*>(ws + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (j < limit) ws[j] = static_cast<int32_t>(v[j]);
+              }
+            }
+          }
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float s0 = __shfl_sync(0xffffffffu, my_sw, j);
+            const float s1 = __shfl_sync(0xffffffffu, my_sw, j + 1);
+            float f0, f1;
+            if constexpr (kMode == kModeGrouped) {
+              f0 = total[chunk * 32 + j];
+              f1 = total[chunk * 32 + j + 1];
+            } else {
+              f0 = __fmul_rn(__int2float_rn(static_cast<int32_t>(v[j])), row_scale);
+              f1 = __fmul_rn(__int2float_rn(static_cast<int32_t>(v[j + 1])), row_scale);
+            }
+            packed[j >> 1] = pack_bf16x2(__fmul_rn(f0, s0), __fmul_rn(f1, s1));
+          }
+          if (row < p.m) {
+            __nv_bfloat16* dst = p.out + static_cast<size_t>(row) * p.n + c0;
+            if (out_vec && limit >= 32) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4)
+                *reinterpret_cast<uint4*>(dst + 2 * j) =
+                    make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (j < limit) {
+                  const uint32_t word = packed[j >> 1];
+                  reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>((j & 1) ? (word >> 16) : (word & 0xffffu));
+                }
+            }
+          }
+        }
+        // this warp is done with the accumulator buffer
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (kCtas == 2) mbar_arrive_cluster(tmem_empty_bar(buf), 0);
+          else mbar_arrive(leader_empty0 + 8u * buf);
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tcgen05_fence_before();
+  __syncthreads();
+  if constexpr (kCtas == 2) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc<kCtas>(tmem_base, 512);
+  }
+}
+
+}  // namespace ci8

@@ -1,0 +1,113 @@
+// Dynamic per-row activation quantizer: BF16 -> signed INT8 codes + one FP32 scale per row
+// (or per row and 4096-channel group).
+//
+//   scale = max(absmax / 127, 1e-20)            IEEE division
+//   code  = clamp(rint_even(x / scale), -127, 127)   IEEE division, round half to even
+//
+// HBM-bound (2 bytes read + 1 byte written per element). Each row is read once: a team of
+// threads (one warp, or one 256-thread CTA for wide rows) holds the row in registers as
+// 16-byte packs across the absmax reduction, then writes 8-byte packs of codes.
+#pragma once
+#include <cuda_bf16.h>
+#include <cstdint>
+
+namespace ci8 {
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+__device__ __forceinline__ int quantize_one(float v, float scale) {
+  return max(-127, min(127, __float2int_rn(__fdiv_rn(v, scale))));
+}
+__device__ __forceinline__ uint32_t quantize_four(uint32_t w0, uint32_t w1, float scale) {
+  const int q0 = quantize_one(bf16_lo(w0), scale), q1 = quantize_one(bf16_hi(w0), scale);
+  const int q2 = quantize_one(bf16_lo(w1), scale), q3 = quantize_one(bf16_hi(w1), scale);
+  return (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | (static_cast<uint32_t>(q3) << 24);
+}
+
+// Row addressing shared by the plain and grouped forms. Output row b (0 <= b < rows):
+//   plain   : input row b
+//   grouped : b = g*M + r reads input row r*G + g  (input [M,G,4096], output [G,M,4096])
+__device__ __forceinline__ int64_t input_row_of(int64_t b, int m, int groups) {
+  return groups > 0 ? (b % m) * groups + b / m : b;
+}
+
+// kTeam threads per row (32 or 256), kPacks 16-byte packs per thread; 256 threads per CTA.
+// Requires: x 16-byte aligned rows (k % 8 == 0, base aligned), q 8-byte aligned.
+template <int kTeam, int kPacks>
+__global__ void __launch_bounds__(256)
+quantize_rows_vec_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
+                         float* __restrict__ scales, int rows, int k, int m, int groups) {
+  constexpr int kRowsPerCta = 256 / kTeam;
+  __shared__ float maxima[8];
+  const int member = threadIdx.x % kTeam;
+  const int64_t out_row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + threadIdx.x / kTeam;
+  const bool active = out_row < rows;
+  const int64_t in_row = active ? input_row_of(out_row, m, groups) : 0;
+  const uint4* src = reinterpret_cast<const uint4*>(x + in_row * k);
+  const int packs_in_row = k >> 3;
+
+  uint4 pack[kPacks];
+  float maximum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPacks; ++i) {
+    const int index = i * kTeam + member;
+    pack[i] = (active && index < packs_in_row) ? __ldg(src + index) : make_uint4(0, 0, 0, 0);
+  }
+#pragma unroll
+  for (int i = 0; i < kPacks; ++i) {
+    const uint32_t w[4] = {pack[i].x, pack[i].y, pack[i].z, pack[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      maximum = fmaxf(maximum, fabsf(bf16_lo(w[j])));
+      maximum = fmaxf(maximum, fabsf(bf16_hi(w[j])));
+    }
+  }
+#pragma unroll
+  for (int mask = 16; mask; mask >>= 1)
+    maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, mask));
+  if constexpr (kTeam == 256) {
+    if ((threadIdx.x & 31) == 0) maxima[threadIdx.x >> 5] = maximum;
+    __syncthreads();
+    maximum = maxima[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) maximum = fmaxf(maximum, maxima[i]);
+  }
+  const float scale = fmaxf(__fdiv_rn(maximum, 127.f), 1e-20f);
+  if (!active) return;
+  if (member == 0) scales[out_row] = scale;
+  uint2* dst = reinterpret_cast<uint2*>(q + out_row * k);
+#pragma unroll
+  for (int i = 0; i < kPacks; ++i) {
+    const int index = i * kTeam + member;
+    if (index < packs_in_row)
+      dst[index] = make_uint2(quantize_four(pack[i].x, pack[i].y, scale),
+                              quantize_four(pack[i].z, pack[i].w, scale));
+  }
+}
+
+// Any width and alignment: one CTA per row, two passes over the row (the second one hits L1/L2).
+__global__ void __launch_bounds__(256)
+quantize_rows_generic_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
+                             float* __restrict__ scales, int k) {
+  __shared__ float maxima[8];
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * k;
+  float maximum = 0.f;
+  for (int c = threadIdx.x; c < k; c += 256)
+    maximum = fmaxf(maximum, fabsf(__uint_as_float(static_cast<uint32_t>(x[base + c]) << 16)));
+#pragma unroll
+  for (int mask = 16; mask; mask >>= 1)
+    maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, mask));
+  if ((threadIdx.x & 31) == 0) maxima[threadIdx.x >> 5] = maximum;
+  __syncthreads();
+  maximum = maxima[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) maximum = fmaxf(maximum, maxima[i]);
+  const float scale = fmaxf(__fdiv_rn(maximum, 127.f), 1e-20f);
+  if (threadIdx.x == 0) scales[blockIdx.x] = scale;
+  for (int c = threadIdx.x; c < k; c += 256)
+    q[base + c] = static_cast<int8_t>(
+        quantize_one(__uint_as_float(static_cast<uint32_t>(x[base + c]) << 16), scale));
+}
+
+}  // namespace ci8

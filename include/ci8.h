@@ -1,0 +1,91 @@
+/*
+ * C ABI of the sm_100a W8A8 linear kernels (libci8.so).
+ *
+ * Every entry point takes raw DEVICE pointers, plain sizes and a CUDA stream, launches on that
+ * stream and returns immediately: no allocation, no host synchronisation, no device-to-host
+ * read, so each call can be captured in a CUDA graph. Outputs are caller-owned and written in
+ * place. Return value: 0 on success, otherwise a cudaError_t value (cudaErrorInvalidValue = 1
+ * for rejected arguments); nothing is thrown across this boundary. ci8_error_string() turns a
+ * code into text. The torch stable-ABI operators in csrc/bindings.cpp are thin wrappers over
+ * these functions; they replace the reference's host launchers declared in csrc/kernels.h.
+ *
+ * Matrices are row-major and contiguous. "BF16" is the 16-bit bfloat16 bit pattern.
+ */
+#ifndef CI8_H_
+#define CI8_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* ci8_stream_t;
+
+/* Replaces quantize_rows (reference csrc/kernels.h:48-49, csrc/kernels.cu:283-292).
+ * x BF16 [m,k] -> codes INT8 [m,k], scales FP32 [m].
+ * scale = max(absmax/127, 1e-20); code = clamp(round_half_even(x/scale), -127, 127). m,k > 0. */
+int ci8_quantize_rows(const void* x, int8_t* codes, float* scales, int m, int k,
+                      ci8_stream_t stream);
+
+/* Replaces quantize_grouped4096 (reference csrc/kernels.h:50-51, csrc/kernels.cu:293-298; C-ABI
+ * precedent benchmarks/cuda/grouped_quant4096.cu:56-62).
+ * x BF16 [m,groups,4096] -> codes INT8 [groups,m,4096], scales FP32 [groups,m]. m == 0 is a
+ * no-op. x must be 16-byte aligned, codes 8-byte aligned. */
+int ci8_quantize_grouped4096(const void* x, int8_t* codes, float* scales, int m, int groups,
+                             ci8_stream_t stream);
+
+/* Replaces fused_channel_mm (reference csrc/kernels.h:27-29, csrc/fused_mm.cu:66-93).
+ * a INT8 [m,k], w INT8 [n,k], a_scale FP32 [m], w_scale BF16 [n] -> out BF16 [m,n],
+ * out = bf16((float(sum_k a*w) * a_scale[row]) * float(w_scale[col])).
+ * k % 32 == 0, k <= 65536, a and w 16-byte aligned. schedule in [0,6]: 0 = automatic; other
+ * values select a tile configuration; every schedule produces identical bits. */
+int ci8_fused_channel_mm(const int8_t* a, const int8_t* w, const float* a_scale,
+                         const void* w_scale, void* out, int m, int n, int k, int schedule,
+                         ci8_stream_t stream);
+
+/* Replaces cutlass_channel_mm (reference csrc/kernels.h:63-65, csrc/cutlass_mm.cu:39-50).
+ * As ci8_fused_channel_mm, and the exact INT32 accumulators are also written to
+ * workspace INT32 [m,n] (caller-owned). */
+int ci8_cutlass_channel_mm(const int8_t* a, const int8_t* w, const float* a_scale,
+                           const void* w_scale, int32_t* workspace, void* out, int m, int n,
+                           int k, ci8_stream_t stream);
+
+/* Replaces channel_mm (reference csrc/kernels.h:56-58, csrc/kernels.cu:299-303).
+ * w UINT8 [n,k] holds signed code + 128. Any n > 0; k % 32 == 0, k <= 65536. */
+int ci8_channel_mm(const int8_t* a, const uint8_t* w, const float* a_scale, const void* w_scale,
+                   void* out, int m, int n, int k, ci8_stream_t stream);
+
+/* Replaces channel_gemv (reference csrc/kernels.h:54-55, csrc/gemv.cu:50-59). W8A16:
+ * x BF16 [m,k], w INT8 [n,k], w_scale BF16 [n] -> out BF16 [m,n] with
+ * out = bf16(sum_k x * bf16(float(w) * float(w_scale))), FP32 accumulation.
+ * 0 < m <= 16 (the reference stops at 8), k % 16 == 0, k <= 65536, w 16-byte aligned. */
+int ci8_channel_gemv(const void* x, const int8_t* w, const void* w_scale, void* out, int m,
+                     int n, int k, ci8_stream_t stream);
+
+/* Grouped-scale W8A8 in one launch. The reference composes this from quantize_grouped4096 and
+ * one fused_channel_mm per group (benchmarks/benchmark_grouped_w8a8.py:100-107); its precedent
+ * for FP32-summed rescaled INT32 partials is benchmarks/cuda/q8_block_int8.cu:44-62.
+ * codes INT8 [groups,m,4096] and scales FP32 [groups,m] as written by
+ * ci8_quantize_grouped4096; w INT8 [n, groups*4096]; w_scale BF16 [n] -> out BF16 [m,n]:
+ * out = bf16((sum over g ascending of float(acc_g) * scales[g,row]) * float(w_scale[col])),
+ * FP32 multiply and add rounded separately. With groups == 1 this is ci8_fused_channel_mm. */
+int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* scales,
+                           const void* w_scale, void* out, int m, int n, int groups,
+                           ci8_stream_t stream);
+
+/* Reads and clears the current device's kernel status word (synchronises the device). Bit 0: a
+ * bounded wait inside a kernel ran past its deadline and the kernel gave up (its output is then
+ * undefined). Returns 0 or a cudaError_t. Not for use during stream capture. */
+int ci8_device_status(unsigned* status);
+
+/* Text for a code returned by any function above. */
+const char* ci8_error_string(int code);
+
+/* Library ABI version (bumped when a signature changes). */
+int ci8_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CI8_H_ */

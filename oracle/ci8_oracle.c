@@ -1,0 +1,100 @@
+/*
+ * Scalar C restatement of the reference's W8A8 linear arithmetic. TEST INFRASTRUCTURE ONLY:
+ * it is a second, independent checker beside oracle/w8a8_ref.py (plain loops, no vector
+ * library), used by the test suite and by the CPU-baseline leg of the benchmark. The shipped
+ * library never links or loads it.
+ *
+ * Parity status: PINNED against the reference's known-answer vectors (tests/golden) and
+ * against oracle/w8a8_ref.py on seeded inputs (tests/test_oracle.py).
+ *
+ * Build: see oracle/Makefile (gcc -O2 -ffp-contract=off).
+ *
+ * Reference anchors (paths inside the reference project):
+ *   quantizer  csrc/kernels.cu:13-35        product   csrc/kernels.cu:95-114, tests/test_cuda_ops.py:488,596
+ *   epilogue   csrc/kernels.cu:120          grouped   csrc/kernels.cu:47-48
+ */
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+
+static float bf16_to_f32(uint16_t h) {
+  uint32_t bits = (uint32_t)h << 16;
+  float f;
+  memcpy(&f, &bits, 4);
+  return f;
+}
+
+/* Round to nearest even, NaN stays NaN (quiet), as cvt.rn.bf16.f32 does. */
+static uint16_t f32_to_bf16(float f) {
+  uint32_t bits;
+  memcpy(&bits, &f, 4);
+  if ((bits & 0x7fffffffu) > 0x7f800000u) return 0x7fffu;
+  bits += 0x7fffu + ((bits >> 16) & 1u);
+  return (uint16_t)(bits >> 16);
+}
+
+/* csrc/kernels.cu:13-35 — absmax, scale = max(absmax/127, 1e-20), round-half-even, clamp ±127. */
+void ci8o_quantize_rows(const uint16_t* x, int8_t* q, float* scales, int m, int k) {
+  for (int r = 0; r < m; ++r) {
+    float maximum = 0.f;
+    for (int c = 0; c < k; ++c) maximum = fmaxf(maximum, fabsf(bf16_to_f32(x[(int64_t)r * k + c])));
+    const float scale = fmaxf(maximum / 127.f, 1e-20f);
+    scales[r] = scale;
+    for (int c = 0; c < k; ++c) {
+      const float v = bf16_to_f32(x[(int64_t)r * k + c]) / scale;
+      int code = 0;
+      if (v == v) { /* __float2int_rn(NaN) == 0 */
+        const float rounded = nearbyintf(v); /* default mode: ties to even */
+        code = rounded > 127.f ? 127 : rounded < -127.f ? -127 : (int)rounded;
+      }
+      q[(int64_t)r * k + c] = (int8_t)code;
+    }
+  }
+}
+
+/* csrc/kernels.cu:47-48,293-298 — input [M,G,4096], output group-major [G,M,4096], scales [G,M]. */
+void ci8o_quantize_grouped4096(const uint16_t* x, int8_t* q, float* scales, int m, int groups) {
+  for (int g = 0; g < groups; ++g)
+    for (int r = 0; r < m; ++r)
+      ci8o_quantize_rows(x + ((int64_t)r * groups + g) * 4096, q + ((int64_t)g * m + r) * 4096,
+                         scales + (int64_t)g * m + r, 1, 4096);
+}
+
+/* tests/test_cuda_ops.py:488,596 — exact INT32 product; UINT8 weights hold code + 128. */
+void ci8o_int_mm(const int8_t* a, const void* w, int w_is_u8, int32_t* acc, int m, int n, int k) {
+  const int8_t* ws = (const int8_t*)w;
+  const uint8_t* wu = (const uint8_t*)w;
+  for (int c = 0; c < n; ++c)
+    for (int r = 0; r < m; ++r) {
+      int32_t sum = 0;
+      for (int i = 0; i < k; ++i) {
+        const int wv = w_is_u8 ? (int)wu[(int64_t)c * k + i] - 128 : (int)ws[(int64_t)c * k + i];
+        sum += (int)a[(int64_t)r * k + i] * wv;
+      }
+      acc[(int64_t)r * n + c] = sum;
+    }
+}
+
+/* csrc/kernels.cu:120 — bf16((float(acc) * sa[row]) * float(sw[col])), two FP32 roundings. */
+void ci8o_epilogue(const int32_t* acc, const float* sa, const uint16_t* sw, uint16_t* out, int m, int n) {
+  for (int r = 0; r < m; ++r)
+    for (int c = 0; c < n; ++c) {
+      volatile float scaled = (float)acc[(int64_t)r * n + c] * sa[r];
+      out[(int64_t)r * n + c] = f32_to_bf16(scaled * bf16_to_f32(sw[c]));
+    }
+}
+
+/* Grouped-scale sum: per group INT32 partial * sa[g,row], FP32 adds in ascending group order,
+ * then the channel scale, then BF16. acc is [G,M,N]. One group reduces to ci8o_epilogue. */
+void ci8o_grouped_epilogue(const int32_t* acc, const float* sa, const uint16_t* sw, uint16_t* out,
+                           int groups, int m, int n) {
+  for (int r = 0; r < m; ++r)
+    for (int c = 0; c < n; ++c) {
+      volatile float total = 0.f;
+      for (int g = 0; g < groups; ++g) {
+        volatile float term = (float)acc[((int64_t)g * m + r) * n + c] * sa[(int64_t)g * m + r];
+        total = g ? total + term : term;
+      }
+      out[(int64_t)r * n + c] = f32_to_bf16(total * bf16_to_f32(sw[c]));
+    }
+}
