@@ -1,0 +1,426 @@
+#!/usr/bin/env python
+"""Benchmark of the W8A8 linear path: one JSON line per run.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A step is one pass of the hot path over one batch of seeded synthetic input: quantize_rows on
+BF16 activations, then the integer GEMM with the fused scale epilogue (and, on more than one
+GPU, the all-gather of the BF16 output). Workloads (shapes of the five benchmark configs):
+
+  sharded        M=16384 K=5120 N=34816, N split over the GPUs        (default, every --gpus)
+  prefill_gate_up  M=4096 K=5120 N=34816       prefill_down   M=4096 K=17408 N=5120
+  decode         M in {1,4,8,16} K=5120 N=34816 (HBM GB/s)            grouped  M=2048 K=8x4096 N=7168
+
+``value`` is whole-job throughput with inputs resident in HBM; ``e2e`` is the same metric through
+the public operators with host buffers (pinned host -> device copy of the activations and
+device -> host copy of the result inside the timed region). ``--impl reference`` times the
+reference's own host restatement of the path (torch on the CPU) on a bounded row sample.
+Inputs are synthetic (no dataset stands behind this path) and larger than L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "consumer-int8-kernels_b200"))
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    "sharded": dict(m=16384, k=5120, n=34816, config="configs[4]"),
+    "prefill_gate_up": dict(m=4096, k=5120, n=34816, config="configs[2]"),
+    "prefill_down": dict(m=4096, k=17408, n=5120, config="configs[2]"),
+    "grouped": dict(m=2048, k=32768, n=7168, groups=8, config="configs[3]"),
+    "decode": dict(m=16, k=5120, n=34816, config="configs[1]"),
+}
+METRIC = "W8A8 GEMM INT8 TOPS (quantize_rows + fused_channel_mm, whole job)"
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0), "fallback"
+
+
+class ClockSampler:
+    """Reads SM clock, power and throttle reasons through NVML while the timed region runs
+    (read-only; nothing is set)."""
+
+    def __init__(self, index: int):
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nvml = None
+
+    def _run(self):
+        n = self.nvml
+        names = {
+            "hw_slowdown": n.nvmlClocksEventReasonHwSlowdown if hasattr(n, "nvmlClocksEventReasonHwSlowdown") else 0x8,
+            "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4, "hw_power_brake": 0x80,
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                mask = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def __enter__(self):
+        if self.nvml:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return dict(sm_mhz=None, sm_max_mhz=self.max_mhz, reasons=[], samples=0)
+        return dict(sm_mhz=statistics.median(self.samples), sm_max_mhz=self.max_mhz,
+                    reasons=sorted(self.reasons), samples=len(self.samples))
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_path(x, w_t, w_scale):
+    """The reference's host restatement of the path: quantize, integer product, epilogue."""
+    from oracle import w8a8_ref as ref
+
+    codes, scales = ref.quantize_rows_ref(x)
+    acc = torch._int_mm(codes, w_t) if codes.shape[0] > 16 else ref.int_mm_fast(codes, w_t.T)
+    return ref.epilogue_ref(acc, scales, w_scale)
+
+
+def cpu_sample(spec, target_seconds: float = 12.0):
+    """Times the CPU path on a bounded row sample of the workload; returns a dict for JSON."""
+    from consumer_int8 import workloads
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    n, k = spec["n"], spec["k"]
+    gen = torch.Generator().manual_seed(0)
+    w, w_scale = workloads.weights(n, k, gen)
+    w_t = w.T.contiguous()
+    probe = 32
+    x = workloads.activations(probe, k, gen)
+    cpu_path(x, w_t, w_scale)
+    t0 = time.perf_counter()
+    cpu_path(x, w_t, w_scale)
+    per_row = (time.perf_counter() - t0) / probe
+    rows = int(max(32, min(spec["m"], target_seconds / 3 / max(per_row, 1e-9))))
+    rows -= rows % 8
+    x = workloads.activations(rows, k, gen)
+    best = min(_timed(lambda: cpu_path(x, w_t, w_scale)) for _ in range(3))
+    tops = 2.0 * rows * n * k / best / 1e12
+    return dict(value=tops, unit="TOPS", cores=torch.get_num_threads(), kind="port",
+                sample=f"{rows} of {spec['m']} rows x N={n} x K={k}, torch CPU (quantize_rows restatement + "
+                       f"torch._int_mm + FP32 epilogue), best of 3, {best:.2f} s"), rows, best
+
+
+def _timed(fn):
+    t0 = time.perf_counter()
+    fn()
+    return time.perf_counter() - t0
+
+
+def run_reference(args, spec, rank):
+    """The reference arm: the host restatement of the path, K timed steps, each over a row sample
+    sized so that warm-up plus K steps take about a minute and a half on this box's cores."""
+    if rank != 0:
+        return
+    from consumer_int8 import workloads
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    n, k = spec["n"], spec["k"]
+    gen = torch.Generator().manual_seed(0)
+    w, w_scale = workloads.weights(n, k, gen)
+    w_t = w.T.contiguous()
+    probe = workloads.activations(32, k, gen)
+    cpu_path(probe, w_t, w_scale)
+    per_row = _timed(lambda: cpu_path(probe, w_t, w_scale)) / 32
+    warmup = max(args.warmup, 1)
+    rows = int(90.0 / (args.steps + warmup) / max(per_row, 1e-9))
+    rows = max(24, min(spec["m"], rows - rows % 8))
+    x = workloads.activations(rows, k, gen)
+    for _ in range(warmup):
+        cpu_path(x, w_t, w_scale)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_path(x, w_t, w_scale)
+    seconds = (time.perf_counter() - t0) / args.steps
+    tops = 2.0 * rows * n * k / seconds / 1e12
+    sample = dict(value=tops, unit="TOPS", cores=torch.get_num_threads(), kind="port",
+                  sample=f"{rows} of {spec['m']} rows x N={n} x K={k} per step, torch CPU (quantize_rows restatement + "
+                         f"torch._int_mm + FP32 epilogue)")
+    line = dict(metric=METRIC, value=tops, unit="TOPS", n_gpus=args.gpus, steps=args.steps, warmup=warmup,
+                ms_per_step=seconds * 1e3, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="int8",
+                data="synthetic", impl="reference",
+                config=dict(workload=f"{args.workload} {spec['config']} M={spec['m']} K={k} N={n}",
+                            step=f"{rows}-row sample per step on the host CPU"),
+                cpu_baseline=sample, e2e=dict(value=tops, unit="TOPS", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_ours(args, spec, rank, world, local_rank):
+    import torch.distributed as dist
+    from consumer_int8 import ops, workloads
+    from consumer_int8.sharded import ColumnShardedLinear, ShardPlan
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    m, n, k = spec["m"], spec["n"], spec["k"]
+    gen = torch.Generator().manual_seed(0)
+    x_host = workloads.activations(m, k, gen).pin_memory()
+    w, w_scale = workloads.weights(n, k, gen)
+    plan = ShardPlan(m, n, k, world, rank, chunks=args.chunks if world > 1 else 1)
+    w_shard, sw_shard = plan.shard_weights(w, w_scale)
+    del w
+    layer = ColumnShardedLinear(plan, w_shard.to(device), sw_shard.to(device), schedule=args.schedule)
+    x = x_host.to(device)
+    out_host = torch.empty(m, plan.shard_n, dtype=torch.bfloat16).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        layer.forward(x)
+    barrier()
+
+    # ---- device-resident timed region (K steps), GEMM timed per launch on the same stream
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    gemm0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    gemm1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    end = torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        for i in range(args.steps):
+            starts[i].record()
+            if world == 1:
+                ops.quantize_rows(x, layer.codes, layer.scales)
+                gemm0[i].record()
+                ops.fused_channel_mm(layer.codes, layer.w, layer.scales, layer.w_scale, layer.local_block(0), args.schedule)
+                gemm1[i].record()
+            else:
+                layer.forward(x)
+        end.record()
+        barrier()
+    step_ms = starts[0].elapsed_time(end) / args.steps
+    gemm_ms = statistics.mean(a.elapsed_time(b) for a, b in zip(gemm0, gemm1)) if world == 1 else None
+    if world > 1:
+        # GEMM-only time of this rank's shard, measured in a separate short loop
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            for c in range(plan.chunks):
+                rows = slice(c * plan.chunk_m, (c + 1) * plan.chunk_m)
+                ops.fused_channel_mm(layer.codes[rows], layer.w, layer.scales[rows], layer.w_scale, layer.local_block(c), args.schedule)
+        b.record()
+        barrier()
+        gemm_ms = a.elapsed_time(b) / 10
+        t = torch.tensor([step_ms, gemm_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        step_ms, gemm_ms = t.tolist()
+
+    # ---- end-to-end region: host activations in, this rank's output block out, every step
+    e2e_steps = max(3, min(args.steps, 10))
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(e2e_steps):
+        x.copy_(x_host, non_blocking=True)
+        gathered = layer.forward(x)
+        for c in range(plan.chunks):
+            out_host[c * plan.chunk_m:(c + 1) * plan.chunk_m].copy_(gathered[c, rank], non_blocking=True)
+    b.record()
+    barrier()
+    e2e_ms = a.elapsed_time(b) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+
+    status = ops.libci8.ci8_device_status
+    import ctypes
+    word = ctypes.c_uint(0)
+    status(ctypes.byref(word))
+    if rank != 0:
+        return
+    peaks, peak_kind = measured_peaks()
+    ops_total = 2.0 * m * n * k
+    tensor_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    gemm_tops = 2.0 * m * plan.shard_n * k / (gemm_ms * 1e-3) / 1e12
+    line = dict(
+        metric=METRIC, value=ops_total / (step_ms * 1e-3) / 1e12, unit="TOPS", n_gpus=world, steps=args.steps,
+        warmup=max(args.warmup, 3), ms_per_step=step_ms, higher_is_better=True, scaling="strong", vs_baseline=None,
+        dtype="int8", data="synthetic",
+        config=dict(workload=f"{args.workload} {spec['config']} M={m} K={k} N={n}", parallelism=f"N-sharded x{world}",
+                    gather="NCCL all-gather of BF16 [M,N/G] blocks" if world > 1 else "none",
+                    row_chunks=plan.chunks, schedule=args.schedule,
+                    l2="inputs larger than L2 (weights+activations+output per step exceed 126 MB); no flush"),
+        roofline=dict(bound="tensor", achieved=gemm_tops, peak=tensor_peak, unit="TFLOP/s", frac=gemm_tops / tensor_peak,
+                      traffic=KERNEL_TRAFFIC.get(args.workload) if world == 1 else None, kernel="gemm_i8_kernel<2,fused>",
+                      note=f"integer ops 2*M*N*K per launch / CUDA-event launch time ({gemm_ms:.3f} ms, per GPU); peak = 2 x "
+                           f"bf16_tflops_sustained of {peak_kind} (INT8 issues at twice the BF16 rate); "
+                           f"vs nominal 4500 dense INT8: {gemm_tops / 4500:.3f}"),
+        e2e=dict(value=ops_total / (e2e_ms * 1e-3) / 1e12, unit="TOPS", h2d_bytes_per_step=x_host.numel() * 2,
+                 d2h_bytes_per_step=out_host.numel() * 2, ms_per_step=e2e_ms, steps=e2e_steps),
+        gpu_launches=args.steps * (1 + plan.chunks), clocks=clocks.summary(), device_status=word.value,
+    )
+    if world == 1:
+        sample, _, _ = cpu_sample(spec)
+        line["cpu_baseline"] = sample
+        if not args.no_extra:
+            line["other_configs"] = other_configs(ops, workloads, device, peaks)
+    print(json.dumps(line), flush=True)
+
+
+# DRAM bytes (read + write) per launch of the dominant kernel from the ncu captures summarised
+# under profiles/ (null until a capture of that workload exists).
+KERNEL_TRAFFIC = {}
+
+
+def _time_graph(fn, launches, replays=5):
+    for _ in range(3):
+        fn(0)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(launches):
+            fn(i)
+    times = []
+    for _ in range(replays):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        b.synchronize()
+        times.append(a.elapsed_time(b) / launches)
+    return statistics.median(times)
+
+
+def other_configs(ops, workloads, device, peaks):
+    """The remaining benchmark configs, each timed as a CUDA graph of back-to-back launches over
+    rotating input copies larger than L2 (the reference's method, benchmarks/microbench.py:15-38)."""
+    results = {}
+    hbm = peaks["hbm_gbs"]
+    tensor_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    gen = torch.Generator().manual_seed(0)
+    # decode: rotate four weight copies (4 x 178 MB) so every launch streams from HBM
+    n, k = 34816, 5120
+    w, w_scale = workloads.weights(n, k, gen)
+    copies = [w.to(device) for _ in range(4)]
+    copies_u8 = [(w.to(torch.int16) + 128).to(torch.uint8).to(device) for _ in range(2)]
+    sw = w_scale.to(device)
+    for m in (1, 4, 8, 16):
+        x = workloads.activations(m, k, gen).to(device)
+        codes = torch.empty(m, k, dtype=torch.int8, device=device)
+        scales = torch.empty(m, device=device)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+        ops.quantize_rows(x, codes, scales)
+        nbytes = n * k + 2 * n + m * k + 4 * m + 2 * m * n
+        ms = _time_graph(lambda i: ops.fused_channel_mm(codes, copies[i % 4], scales, sw, out, 0), 40)
+        ms_u8 = _time_graph(lambda i: ops.channel_mm(codes, copies_u8[i % 2], scales, sw, out), 40)
+        ms_q = _time_graph(lambda i: (ops.quantize_rows(x, codes, scales), ops.fused_channel_mm(codes, copies[i % 4], scales, sw, out, 0)), 40)
+        ms_gemv = _time_graph(lambda i: ops.channel_gemv(x, copies[i % 4], sw, out), 20)
+        results[f"decode_m{m}"] = dict(us=ms * 1e3, gbs=nbytes / ms / 1e6, frac_hbm=nbytes / ms / 1e6 / hbm,
+                                       channel_mm_u8_us=ms_u8 * 1e3, with_quantize_us=ms_q * 1e3,
+                                       channel_gemv_us=ms_gemv * 1e3,
+                                       channel_gemv_gbs=(n * k + 2 * n + 2 * m * k + 2 * m * n) / ms_gemv / 1e6)
+    del copies, copies_u8
+    for name in ("prefill_gate_up", "prefill_down"):
+        spec = WORKLOADS[name]
+        m, n, k = spec["m"], spec["n"], spec["k"]
+        w, w_scale = workloads.weights(n, k, gen)
+        wd, sw = w.to(device), w_scale.to(device)
+        x = workloads.activations(m, k, gen).to(device)
+        codes = torch.empty(m, k, dtype=torch.int8, device=device)
+        scales = torch.empty(m, device=device)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+        ops.quantize_rows(x, codes, scales)
+        ms = _time_graph(lambda i: ops.fused_channel_mm(codes, wd, scales, sw, out, 0), 20)
+        xs = [x.clone() for _ in range(4)]
+        ms_q = _time_graph(lambda i: ops.quantize_rows(xs[i % 4], codes, scales), 40)
+        tops = 2.0 * m * n * k / ms / 1e9
+        results[name] = dict(gemm_ms=ms, tops=tops, frac_tensor=tops / tensor_peak, frac_nominal_4500=tops / 4500,
+                             quantize_us=ms_q * 1e3, quantize_gbs=(3 * m * k + 4 * m) / ms_q / 1e6)
+        del wd, x, xs, out, codes
+    spec = WORKLOADS["grouped"]
+    m, n, groups = spec["m"], spec["n"], spec["groups"]
+    inputs = workloads.grouped_inputs(m, n, groups, seed=0)
+    xs = [inputs.x.to(device) for _ in range(2)]
+    wd, sw = inputs.w.to(device), inputs.w_scale.to(device)
+    codes = torch.empty(groups, m, 4096, dtype=torch.int8, device=device)
+    scales = torch.empty(groups, m, device=device)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+    ms_q = _time_graph(lambda i: ops.quantize_grouped4096(xs[i % 2], codes, scales), 20)
+    ms = _time_graph(lambda i: ops.grouped_channel_mm(codes, wd, scales, sw, out), 10)
+    tops = 2.0 * m * n * groups * 4096 / ms / 1e9
+    results["grouped"] = dict(gemm_ms=ms, tops=tops, frac_tensor=tops / tensor_peak, frac_nominal_4500=tops / 4500,
+                              quantize_us=ms_q * 1e3, quantize_gbs=(3 * m * groups * 4096 + 4 * m * groups) / ms_q / 1e6)
+    return results
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=100)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--workload", choices=["sharded", "prefill_gate_up", "prefill_down"], default="sharded")
+    parser.add_argument("--schedule", type=int, default=0)
+    parser.add_argument("--chunks", type=int, default=4, help="row chunks whose gather overlaps the next GEMM (N>1)")
+    parser.add_argument("--no-extra", action="store_true", help="skip the other benchmark configs")
+    args = parser.parse_args()
+    spec = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, spec, rank)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, spec, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

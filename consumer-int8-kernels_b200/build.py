@@ -33,6 +33,16 @@ STABLE_DEFINES = [
 ]
 
 
+def _host_cxx() -> str:
+    """The distribution's g++ (dynamic libstdc++). A toolchain wrapper that links libstdc++
+    statically would put a second, uninitialised copy of the iostream/locale state inside
+    _C.so, and the first formatted error message would crash; CI8_CXX overrides the choice."""
+    override = os.environ.get("CI8_CXX")
+    if override:
+        return override
+    return "/usr/bin/g++" if Path("/usr/bin/g++").exists() else "g++"
+
+
 def _newer(target: Path, sources: list[Path]) -> bool:
     if not target.exists():
         return False
@@ -73,7 +83,7 @@ def build_bindings(force: bool = False) -> Path:
         Path(sysconfig.get_paths()["include"]),
     ]
     cmd = [
-        os.environ.get("CXX", "g++"), "-O3", "-std=c++17", "-fPIC", "-shared", *STABLE_DEFINES,
+        _host_cxx(), "-O3", "-std=c++17", "-fPIC", "-shared", *STABLE_DEFINES,
         *[f"-I{p}" for p in includes],
         "-o", target, CSRC / "bindings.cpp",
         f"-L{PKG}", "-lci8", "-Wl,-rpath,$ORIGIN",

@@ -1,0 +1,142 @@
+"""Output-channel (N) sharding of the W8A8 linear over the GPUs of one box.
+
+The reference has no collective of its own; its serving stack runs these projections column-
+parallel and gathers the result (benchmarks/microbench.py:187 "column parallel + gather").
+Here rank r owns ``w[r*N/G:(r+1)*N/G]`` and its channel scales, the activations are replicated,
+every rank quantizes them itself (cheap next to the GEMM) and computes a BF16 ``[M, N/G]`` column
+block, and one NCCL all-gather of that BF16 block — nothing else crosses NVLink — leaves the
+whole output on every rank.
+
+Layout of the gathered output: ``[chunks, G, M/chunks, N/G]``. Column blocks of a row-major
+``[M, N]`` matrix are not contiguous, so each rank's block is kept contiguous instead and the
+gather is done in place (a rank writes its block straight into its slot). ``chunks > 1`` splits
+the rows so that the gather of a finished row chunk overlaps the GEMM of the next one on a
+second stream. ``ShardPlan.row_major`` gives the ``[M, N]`` view as a copy when a caller needs it.
+
+The bookkeeping (``ShardPlan``) is plain Python and is tested with CPU ranks over gloo; the
+device work goes through ``consumer_int8.ops`` and fails loudly without the CUDA extension.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class ShardPlan:
+    m: int
+    n: int
+    k: int
+    world: int
+    rank: int
+    chunks: int = 1
+
+    def __post_init__(self):
+        if self.world <= 0 or not 0 <= self.rank < self.world:
+            raise ValueError(f"rank {self.rank} outside world of {self.world}")
+        if self.n % self.world:
+            raise ValueError(f"N={self.n} does not split evenly over {self.world} ranks")
+        if (self.n // self.world) % 4:
+            raise ValueError("each shard must keep N % 4 == 0 (fused_channel_mm geometry)")
+        if self.chunks <= 0 or self.m % self.chunks:
+            raise ValueError(f"M={self.m} does not split into {self.chunks} row chunks")
+
+    @property
+    def shard_n(self) -> int:
+        return self.n // self.world
+
+    @property
+    def chunk_m(self) -> int:
+        return self.m // self.chunks
+
+    @property
+    def channels(self) -> slice:
+        """The output channels this rank owns."""
+        return slice(self.rank * self.shard_n, (self.rank + 1) * self.shard_n)
+
+    @property
+    def gathered_shape(self) -> tuple[int, int, int, int]:
+        return (self.chunks, self.world, self.chunk_m, self.shard_n)
+
+    @property
+    def gather_bytes_received(self) -> int:
+        """BF16 bytes each rank receives per call."""
+        return 2 * self.m * self.shard_n * (self.world - 1)
+
+    def shard_weights(self, w: torch.Tensor, w_scale: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        if w.shape[0] != self.n or w_scale.shape[0] != self.n:
+            raise ValueError("weight or scale does not have N rows")
+        return w[self.channels].contiguous(), w_scale[self.channels].contiguous()
+
+    def row_major(self, gathered: torch.Tensor) -> torch.Tensor:
+        """[chunks, G, M/chunks, N/G] -> [M, N] (a copy)."""
+        if tuple(gathered.shape) != self.gathered_shape:
+            raise ValueError(f"expected {self.gathered_shape}, got {tuple(gathered.shape)}")
+        return gathered.permute(0, 2, 1, 3).reshape(self.m, self.n)
+
+
+class ColumnShardedLinear:
+    """quantize_rows -> fused_channel_mm on this rank's channels -> all-gather of the BF16 block.
+
+    All buffers are allocated once here; ``forward`` allocates nothing.
+    """
+
+    def __init__(self, plan: ShardPlan, w_shard: torch.Tensor, w_scale_shard: torch.Tensor,
+                 group: dist.ProcessGroup | None = None, schedule: int = 0, operators=None):
+        if operators is None:
+            from . import ops as operators  # the compiled operators; there is no fallback
+
+        self.ops = operators   # tests of the host logic inject a stand-in here
+        self.plan = plan
+        self.group = group
+        self.schedule = schedule
+        if tuple(w_shard.shape) != (plan.shard_n, plan.k) or w_shard.dtype != torch.int8:
+            raise ValueError("w_shard must be INT8 [N/G, K]")
+        self.w = w_shard
+        self.w_scale = w_scale_shard
+        device = w_shard.device
+        self.codes = torch.empty(plan.m, plan.k, dtype=torch.int8, device=device)
+        self.scales = torch.empty(plan.m, dtype=torch.float32, device=device)
+        self.gathered = torch.empty(plan.gathered_shape, dtype=torch.bfloat16, device=device)
+        overlap = plan.chunks > 1 and plan.world > 1 and device.type == "cuda"
+        self.comm_stream = torch.cuda.Stream(device=device) if overlap else None
+        self._chunk_done = [torch.cuda.Event() for _ in range(plan.chunks)] if self.comm_stream else []
+
+    def local_block(self, chunk: int = 0) -> torch.Tensor:
+        return self.gathered[chunk, self.plan.rank]
+
+    def compute(self, x: torch.Tensor) -> None:
+        """Quantize and run this rank's GEMM (no communication)."""
+        plan = self.plan
+        self.ops.quantize_rows(x, self.codes, self.scales)
+        for c in range(plan.chunks):
+            rows = slice(c * plan.chunk_m, (c + 1) * plan.chunk_m)
+            self.ops.fused_channel_mm(self.codes[rows], self.w, self.scales[rows], self.w_scale,
+                                      self.local_block(c), self.schedule)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        plan = self.plan
+        if plan.world == 1:
+            self.compute(x)
+            return self.gathered
+        self.ops.quantize_rows(x, self.codes, self.scales)
+        main = torch.cuda.current_stream() if self.comm_stream is not None else None
+        for c in range(plan.chunks):
+            rows = slice(c * plan.chunk_m, (c + 1) * plan.chunk_m)
+            self.ops.fused_channel_mm(self.codes[rows], self.w, self.scales[rows], self.w_scale,
+                                      self.local_block(c), self.schedule)
+            flat = self.gathered[c].view(plan.world * plan.chunk_m, plan.shard_n)
+            mine = self.local_block(c)
+            if self.comm_stream is None:
+                dist.all_gather_into_tensor(flat, mine, group=self.group)
+            else:
+                self._chunk_done[c].record(main)
+                with torch.cuda.stream(self.comm_stream):
+                    self.comm_stream.wait_event(self._chunk_done[c])
+                    dist.all_gather_into_tensor(flat, mine, group=self.group)
+        if self.comm_stream is not None:
+            main.wait_stream(self.comm_stream)
+        return self.gathered

@@ -15,9 +15,9 @@
 
 using torch::stable::Tensor;
 using torch::headeronly::ScalarType;
-using torch::stable::detail::to;
 
 namespace {
+using torch::stable::detail::to;
 constexpr int64_t kIntMax = std::numeric_limits<int>::max();
 
 void check(const Tensor& t, ScalarType dtype, int device) {

@@ -100,6 +100,11 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   GemmParams p = base;
   p.tiles_m = (p.m + Cfg::kBlockM * kCtas - 1) / (Cfg::kBlockM * kCtas);
   p.tiles_n = (p.n + Cfg::kChannelsPerTile - 1) / Cfg::kChannelsPerTile;
+  // rows of A per raster group: about 32 MiB of activations, so they stay in L2
+  const long long group_rows = (32ll << 20) / (static_cast<long long>(p.k) * p.groups);
+  p.group_m = static_cast<int>(group_rows / (Cfg::kBlockM * kCtas));
+  if (p.group_m < 1) p.group_m = 1;
+  if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
   CUtensorMap map_a, map_w;
   err = make_map(&map_a, a, static_cast<uint64_t>(p.m) * p.groups, p.k, Cfg::kBlockM);
   if (err != cudaSuccess) return err;
@@ -313,7 +318,7 @@ int ci8_fused_channel_mm(const int8_t* a, const int8_t* w, const float* a_scale,
     return launch_decode<false>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, k, 1, 0, 0};
+               m, n, k, 1, 0, 0, 0};
   // schedule 0: pairs of CTAs once there is more than one 128-row block; odd values force the
   // single-CTA tile, even values the two-CTA tile. All give identical bits.
   const bool pair = schedule == 0 ? m > 128 : (schedule % 2 == 0);
@@ -332,7 +337,7 @@ int ci8_cutlass_channel_mm(const int8_t* a, const int8_t* w, const float* a_scal
     return launch_decode<false>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), workspace,
-               m, n, k, 1, 0, 0};
+               m, n, k, 1, 0, 0, 0};
   return m > 128 ? launch_gemm<2, kModeWorkspace>(a, w, p, s) : launch_gemm<1, kModeWorkspace>(a, w, p, s);
 }
 
@@ -347,7 +352,7 @@ int ci8_channel_mm(const int8_t* a, const uint8_t* w, const float* a_scale, cons
     return launch_decode<true>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, k, 1, 0, 0};
+               m, n, k, 1, 0, 0, 0};
   return launch_gemm<1, kModeBiased>(a, w, p, s);
 }
 
@@ -371,7 +376,7 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
       static_cast<long long>(m) * n > INT32_MAX || !aligned(codes, 16) || !aligned(w, 16))
     return kInvalid;
   GemmParams p{scales, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, 4096, groups, 0, 0};
+               m, n, 4096, groups, 0, 0, 0};
   return launch_gemm<1, kModeGrouped>(codes, w, p, reinterpret_cast<cudaStream_t>(stream));
 }
 

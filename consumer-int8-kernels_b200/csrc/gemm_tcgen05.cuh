@@ -40,6 +40,7 @@ struct GemmParams {
   int m, n, k;                // k = K per group
   int groups;                 // 1 unless grouped
   int tiles_m, tiles_n;
+  int group_m;                // row tiles per raster group (L2 reuse of the A rows)
 };
 
 template <int kCtas, int kMode>
@@ -63,6 +64,19 @@ struct GemmConfig {
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + align slack
   static_assert(kMode != kModeBiased || kCtas == 1, "biased weights use the single-CTA tile");
 };
+
+// Tile order: row tiles are walked in groups of group_m; inside a group the row tile index runs
+// fastest, then the channel tile. One wave of CTAs then touches a bounded set of A rows (which
+// stay in L2 while the weights stream past) instead of every row of a tall A.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mt, int& nt) {
+  const int per_group = p.group_m * p.tiles_n;
+  const int group = tile / per_group;
+  const int within = tile - group * per_group;
+  const int first_m = group * p.group_m;
+  const int rows_in_group = min(p.group_m, p.tiles_m - first_m);
+  mt = first_m + within % rows_in_group;
+  nt = within / rows_in_group;
+}
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -146,7 +160,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t leader_full0 = kCtas == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
       bool ok = true;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-        const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
+        int mt, nt;
+        tile_coords(p, tile, mt, nt);
         const int a_row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM;
         const int w_row = nt * Cfg::kChannelsPerTile + rank * Cfg::kBRowsSmem;
         for (int g = 0; ok && g < p.groups; ++g) {
@@ -225,7 +240,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     bool ok = true;
     float total[kMode == kModeGrouped ? Cfg::kColsPerEpiWarp : 1];
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-      const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
+      int mt, nt;
+      tile_coords(p, tile, mt, nt);
       const int row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM + quarter * 32 + lane;
       const int n0 = nt * Cfg::kChannelsPerTile;
       for (int g = 0; g < p.groups; ++g, ++acc_iter) {

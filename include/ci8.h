@@ -74,6 +74,14 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
                            const void* w_scale, void* out, int m, int n, int groups,
                            ci8_stream_t stream);
 
+/* The decode (m <= 16) kernel behind ci8_fused_channel_mm / ci8_cutlass_channel_mm /
+ * ci8_channel_mm with the split-K factor forced to 1, 2 or 4 instead of chosen from the shape.
+ * No counterpart in the reference; it exists so that tests can show the result does not depend
+ * on the split. weights_biased != 0: w is UINT8 code+128. workspace may be NULL. */
+int ci8_decode_mm_split(const int8_t* a, const void* w, const float* a_scale, const void* w_scale,
+                        int32_t* workspace, void* out, int m, int n, int k, int split,
+                        int weights_biased, ci8_stream_t stream);
+
 /* Reads and clears the current device's kernel status word (synchronises the device). Bit 0: a
  * bounded wait inside a kernel ran past its deadline and the kernel gave up (its output is then
  * undefined). Returns 0 or a cudaError_t. Not for use during stream capture. */

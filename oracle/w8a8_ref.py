@@ -53,7 +53,8 @@ def quantize_rows_ref(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """
     assert x.dtype == torch.bfloat16 and x.dim() == 2
     value = x.float()
-    absmax = value.abs().amax(dim=1)
+    # fmaxf() returns the other operand when one is NaN, so a NaN never enters the row maximum.
+    absmax = torch.nan_to_num(value.abs(), nan=0.0, posinf=float("inf")).amax(dim=1)
     scale = torch.maximum(absmax / torch.full_like(absmax, 127.0),
                           torch.full_like(absmax, 1e-20))
     quotient = value / scale[:, None].expand_as(value)

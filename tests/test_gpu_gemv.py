@@ -1,0 +1,41 @@
+"""channel_gemv (W8A16) against the reference's FP64 oracle, with the reference's tolerances
+(tests/test_gemv.py:10-33): atol 0.004, rtol 0.008, relative L2 error below 0.003."""
+import pytest
+import torch
+
+from gpu_common import DEV
+from oracle import w8a8_ref as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 8, 13, 16])
+@pytest.mark.parametrize("n,k", [(37, 528), (512, 5120), (1000, 17408)])
+def test_w8a16_small_batch_matches_bf16_dequantized_linear(ops, m, n, k):
+    torch.manual_seed(134)
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    weight = torch.randint(-127, 128, (n, k), device=DEV, dtype=torch.int8)
+    scale = (torch.rand(n, device=DEV) * 0.002).bfloat16()
+    out = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    ops.channel_gemv(x, weight, scale, out)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.channel_gemv(x, weight, scale, out)
+    x.mul_(0.75)
+    graph.replay()
+    reference = ref.channel_gemv_fp64(x.cpu(), weight.cpu(), scale.cpu())
+    actual = out.cpu()
+    torch.testing.assert_close(actual, reference, atol=0.004, rtol=0.008)
+    error = (actual.float() - reference.float()).norm() / reference.float().norm()
+    assert error.item() < 0.003
+
+
+def test_gemv_rejects_unsupported_geometry(ops):
+    x = torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 64, dtype=torch.int8, device=DEV)
+    scale = torch.ones(8, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError, match="GEMV geometry"):
+        ops.channel_gemv(x, w, scale, torch.empty(17, 8, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(RuntimeError, match="GEMV geometry"):      # k % 16
+        ops.channel_gemv(x[:1, :40].contiguous(), w[:, :40].contiguous(), scale,
+                         torch.empty(1, 8, dtype=torch.bfloat16, device=DEV))

@@ -1,0 +1,62 @@
+"""Grouped-scale W8A8 (benchmark config 3): quantize_grouped4096 followed by the one-launch
+grouped GEMM, bit for bit against the CPU checker; and the reference-faithful composition
+(one fused_channel_mm per group, benchmarks/benchmark_grouped_w8a8.py:100-107)."""
+import pytest
+import torch
+
+from consumer_int8 import workloads
+from gpu_common import DEV, assert_bit_equal, device_status, guarded
+from oracle import w8a8_ref as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("m,n,groups", [(128, 256, 1), (130, 260, 2), (300, 512, 3), (1, 8, 4), (513, 1000, 8)])
+def test_grouped_channel_mm_matches_checker(ops, m, n, groups):
+    inputs = workloads.grouped_inputs(m, n, groups, seed=m + groups)
+    x = inputs.x.to(DEV)
+    codes = torch.empty(groups, m, 4096, dtype=torch.int8, device=DEV)
+    scales = torch.empty(groups, m, device=DEV)
+    ops.quantize_grouped4096(x, codes, scales)
+    want_codes, want_scales = ref.quantize_grouped4096_ref(inputs.x)
+    assert_bit_equal(codes, want_codes, "codes")
+    assert_bit_equal(scales, want_scales, "scales")
+    out, check = guarded((m, n), torch.bfloat16, float("nan"))
+    ops.grouped_channel_mm(codes, inputs.w.to(DEV), scales, inputs.w_scale.to(DEV), out)
+    want = ref.grouped_channel_mm_ref(want_codes, want_scales, inputs.w, inputs.w_scale, fast=True)
+    assert_bit_equal(out, want, "grouped out")
+    check()
+    assert device_status(ops) == 0
+
+
+def test_one_group_equals_fused_channel_mm(ops):
+    inputs = workloads.grouped_inputs(200, 512, 1, seed=2)
+    codes, scales = ref.quantize_grouped4096_ref(inputs.x)
+    grouped = torch.empty(200, 512, dtype=torch.bfloat16, device=DEV)
+    fused = torch.empty_like(grouped)
+    ops.grouped_channel_mm(codes.to(DEV), inputs.w.to(DEV), scales.to(DEV), inputs.w_scale.to(DEV), grouped)
+    ops.fused_channel_mm(codes[0].to(DEV), inputs.w.to(DEV), scales[0].to(DEV), inputs.w_scale.to(DEV), fused)
+    assert_bit_equal(grouped, fused, "one group")
+
+
+def test_per_group_fused_calls_on_group_slices(ops):
+    """What the reference does today: G independent GEMMs on codes[g] against that group's
+    columns of the weight (here each group's slice is made contiguous, as the reference's
+    per-group weight tensors are)."""
+    m, n, groups = 96, 256, 4
+    inputs = workloads.grouped_inputs(m, n, groups, seed=11)
+    codes, scales = ref.quantize_grouped4096_ref(inputs.x)
+    for g in range(groups):
+        wg = inputs.w[:, g * 4096:(g + 1) * 4096].contiguous()
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        ops.fused_channel_mm(codes[g].to(DEV), wg.to(DEV), scales[g].to(DEV), inputs.w_scale.to(DEV), out, 0)
+        _, want = ref.fused_channel_mm_ref(codes[g], wg, scales[g], inputs.w_scale, fast=True)
+        assert_bit_equal(out, want, f"group {g}")
+
+
+def test_grouped_rejects_bad_geometry(ops):
+    codes = torch.zeros(2, 4, 4096, dtype=torch.int8, device=DEV)
+    w = torch.zeros(8, 4096, dtype=torch.int8, device=DEV)       # K for one group only
+    with pytest.raises(RuntimeError, match="geometry"):
+        ops.grouped_channel_mm(codes, w, torch.ones(2, 4, device=DEV), torch.ones(8, dtype=torch.bfloat16, device=DEV),
+                               torch.empty(4, 8, dtype=torch.bfloat16, device=DEV))
