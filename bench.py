@@ -388,13 +388,47 @@ def other_configs(ops, workloads, device, peaks):
     return results
 
 
+def profile_only(args, spec):
+    """A few launches of one workload's kernels on cuda:0, nothing timed: the command line that
+    ncu captures are taken from (weights rotate over copies larger than L2 for the decode case)."""
+    from consumer_int8 import ops, workloads
+
+    device = torch.device("cuda", 0)
+    m, n, k = spec["m"], spec["n"], spec["k"]
+    if args.workload == "grouped":
+        inputs = workloads.grouped_inputs(m, n, spec["groups"], seed=0)
+        x, w, sw = inputs.x.to(device), inputs.w.to(device), inputs.w_scale.to(device)
+        codes = torch.empty(spec["groups"], m, 4096, dtype=torch.int8, device=device)
+        scales = torch.empty(spec["groups"], m, device=device)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+        for _ in range(args.steps):
+            ops.quantize_grouped4096(x, codes, scales)
+            ops.grouped_channel_mm(codes, w, scales, sw, out)
+    else:
+        inputs = workloads.linear_inputs(m, n, k, seed=0)
+        x, sw = inputs.x.to(device), inputs.w_scale.to(device)
+        copies = [inputs.w.to(device) for _ in range(3 if args.workload == "decode" else 1)]
+        codes = torch.empty(m, k, dtype=torch.int8, device=device)
+        scales = torch.empty(m, device=device)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+        for i in range(args.steps):
+            ops.quantize_rows(x, codes, scales)
+            ops.fused_channel_mm(codes, copies[i % len(copies)], scales, sw, out, args.schedule)
+            if args.workload == "decode":
+                ops.channel_gemv(x, copies[i % len(copies)], sw, out)
+    torch.cuda.synchronize()
+    print(json.dumps(dict(profile_only=args.workload, launches=args.steps)), flush=True)
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    parser.add_argument("--workload", choices=["sharded", "prefill_gate_up", "prefill_down"], default="sharded")
+    parser.add_argument("--workload", choices=list(WORKLOADS), default="sharded")
+    parser.add_argument("--profile-only", action="store_true",
+                        help="run --steps launches of the workload's kernels with no timing (for ncu captures)")
     parser.add_argument("--schedule", type=int, default=0)
     parser.add_argument("--chunks", type=int, default=4, help="row chunks whose gather overlaps the next GEMM (N>1)")
     parser.add_argument("--no-extra", action="store_true", help="skip the other benchmark configs")
@@ -406,6 +440,12 @@ def main():
     if args.impl == "reference":
         run_reference(args, spec, rank)
         return
+    if args.profile_only:
+        profile_only(args, spec)
+        return
+    if args.workload in ("decode", "grouped"):
+        raise SystemExit("the decode and grouped workloads are timed inside the default run (other_configs) "
+                         "or launched with --profile-only")
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     if world > 1:

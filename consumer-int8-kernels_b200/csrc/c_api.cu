@@ -222,17 +222,13 @@ cudaError_t launch_quantize(const void* x, int8_t* q, float* s, int rows, int k,
                             cudaStream_t stream) {
   const bool vector_ok = k % 8 == 0 && aligned(x, 16) && aligned(q, 8);
   const int packs = k / 8;
-  if (vector_ok && packs <= 32 * 32 && rows >= 64) {
-    // one warp per row: up to 32 packs per lane
+  if (vector_ok && packs <= 32 * 4 && rows >= 64) {
+    // narrow rows (K <= 1024): one warp per row, eight rows per CTA
     const int per_lane = (packs + 31) / 32;
 #define CI8_WARP(P) launch_quantize_vec<32, P>(x, q, s, rows, k, m, groups, stream)
-    if (per_lane <= 4) CI8_WARP(4);
-    else if (per_lane <= 8) CI8_WARP(8);
-    else if (per_lane <= 12) CI8_WARP(12);
-    else if (per_lane <= 16) CI8_WARP(16);
-    else if (per_lane <= 20) CI8_WARP(20);
-    else if (per_lane <= 24) CI8_WARP(24);
-    else CI8_WARP(32);
+    if (per_lane <= 1) CI8_WARP(1);
+    else if (per_lane <= 2) CI8_WARP(2);
+    else CI8_WARP(4);
 #undef CI8_WARP
   } else if (vector_ok && packs <= 256 * 32) {
     // one 256-thread CTA per row
@@ -377,7 +373,8 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
     return kInvalid;
   GemmParams p{scales, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
                m, n, 4096, groups, 0, 0, 0};
-  return launch_gemm<1, kModeGrouped>(codes, w, p, reinterpret_cast<cudaStream_t>(stream));
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return m > 128 ? launch_gemm<2, kModeGrouped>(codes, w, p, s) : launch_gemm<1, kModeGrouped>(codes, w, p, s);
 }
 
 // Test hook: the decode kernel with a forced split-K factor (1, 2 or 4); weights_biased != 0

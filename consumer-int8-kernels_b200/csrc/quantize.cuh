@@ -1,12 +1,19 @@
 // Dynamic per-row activation quantizer: BF16 -> signed INT8 codes + one FP32 scale per row
 // (or per row and 4096-channel group).
 //
-//   scale = max(absmax / 127, 1e-20)            IEEE division
+//   scale = max(absmax / 127, 1e-20)                 IEEE division
 //   code  = clamp(rint_even(x / scale), -127, 127)   IEEE division, round half to even
 //
 // HBM-bound (2 bytes read + 1 byte written per element). Each row is read once: a team of
-// threads (one warp, or one 256-thread CTA for wide rows) holds the row in registers as
+// threads (one warp for narrow rows, one 256-thread CTA otherwise) holds the row in registers as
 // 16-byte packs across the absmax reduction, then writes 8-byte packs of codes.
+//
+// The per-element IEEE division would make the kernel instruction-bound, so the common case
+// takes a short path that provably gives the same bits: q' = x * (1/scale) is within 2.3e-5 of
+// the correctly rounded quotient for |q| <= 127, so whenever q' is farther than 5e-5 from a
+// half-integer, rint(q') equals rint of the IEEE quotient; rounding and the integer conversion
+// are one FADD with 1.5*2^23 (the low byte of the sum is the two's-complement code). A pack that
+// holds a value too close to a tie, a NaN or an infinity is redone with the IEEE division.
 #pragma once
 #include <cuda_bf16.h>
 #include <cstdint>
@@ -16,13 +23,47 @@ namespace ci8 {
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
+// The reference arithmetic, literally.
 __device__ __forceinline__ int quantize_one(float v, float scale) {
   return max(-127, min(127, __float2int_rn(__fdiv_rn(v, scale))));
 }
-__device__ __forceinline__ uint32_t quantize_four(uint32_t w0, uint32_t w1, float scale) {
+__device__ __forceinline__ uint32_t quantize_four_exact(uint32_t w0, uint32_t w1, float scale) {
   const int q0 = quantize_one(bf16_lo(w0), scale), q1 = quantize_one(bf16_hi(w0), scale);
   const int q2 = quantize_one(bf16_lo(w1), scale), q3 = quantize_one(bf16_hi(w1), scale);
   return (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | (static_cast<uint32_t>(q3) << 24);
+}
+
+constexpr float kRoundMagic = 12582912.f;   // 1.5 * 2^23
+constexpr float kTieGuard = 0.49995f;       // |q' - rint(q')| below this: no tie within the error bound
+
+// Short path for one value: returns the FADD result whose low byte is the code and clears `safe`
+// when the value is not provably away from a rounding tie (NaN compares false, so NaN and
+// inf * 0 land on the exact path too).
+__device__ __forceinline__ uint32_t quantize_fast(float v, float inverse, bool& safe) {
+  const float q = __fmul_rn(v, inverse);
+  const float shifted = __fadd_rn(q, kRoundMagic);
+  const float rounded = __fsub_rn(shifted, kRoundMagic);
+  safe = safe && (fabsf(__fsub_rn(q, rounded)) < kTieGuard);
+  return __float_as_uint(shifted);
+}
+
+// Eight BF16 values (one 16-byte pack) -> eight codes (8 bytes).
+__device__ __forceinline__ uint2 quantize_pack(const uint4& pack, float scale, float inverse) {
+  bool safe = true;
+  const uint32_t t0 = quantize_fast(bf16_lo(pack.x), inverse, safe);
+  const uint32_t t1 = quantize_fast(bf16_hi(pack.x), inverse, safe);
+  const uint32_t t2 = quantize_fast(bf16_lo(pack.y), inverse, safe);
+  const uint32_t t3 = quantize_fast(bf16_hi(pack.y), inverse, safe);
+  const uint32_t t4 = quantize_fast(bf16_lo(pack.z), inverse, safe);
+  const uint32_t t5 = quantize_fast(bf16_hi(pack.z), inverse, safe);
+  const uint32_t t6 = quantize_fast(bf16_lo(pack.w), inverse, safe);
+  const uint32_t t7 = quantize_fast(bf16_hi(pack.w), inverse, safe);
+  if (safe) {
+    const uint32_t lo = __byte_perm(__byte_perm(t0, t1, 0x0040), __byte_perm(t2, t3, 0x0040), 0x5410);
+    const uint32_t hi = __byte_perm(__byte_perm(t4, t5, 0x0040), __byte_perm(t6, t7, 0x0040), 0x5410);
+    return make_uint2(lo, hi);
+  }
+  return make_uint2(quantize_four_exact(pack.x, pack.y, scale), quantize_four_exact(pack.z, pack.w, scale));
 }
 
 // Row addressing shared by the plain and grouped forms. Output row b (0 <= b < rows):
@@ -33,7 +74,7 @@ __device__ __forceinline__ int64_t input_row_of(int64_t b, int m, int groups) {
 }
 
 // kTeam threads per row (32 or 256), kPacks 16-byte packs per thread; 256 threads per CTA.
-// Requires: x 16-byte aligned rows (k % 8 == 0, base aligned), q 8-byte aligned.
+// Requires 16-byte aligned rows of x (k % 8 == 0, base aligned) and 8-byte aligned q.
 template <int kTeam, int kPacks>
 __global__ void __launch_bounds__(256)
 quantize_rows_vec_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
@@ -74,15 +115,14 @@ quantize_rows_vec_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
     for (int i = 1; i < 8; ++i) maximum = fmaxf(maximum, maxima[i]);
   }
   const float scale = fmaxf(__fdiv_rn(maximum, 127.f), 1e-20f);
+  const float inverse = __fdiv_rn(1.f, scale);
   if (!active) return;
   if (member == 0) scales[out_row] = scale;
   uint2* dst = reinterpret_cast<uint2*>(q + out_row * k);
 #pragma unroll
   for (int i = 0; i < kPacks; ++i) {
     const int index = i * kTeam + member;
-    if (index < packs_in_row)
-      dst[index] = make_uint2(quantize_four(pack[i].x, pack[i].y, scale),
-                              quantize_four(pack[i].z, pack[i].w, scale));
+    if (index < packs_in_row) dst[index] = quantize_pack(pack[i], scale, inverse);
   }
 }
 
