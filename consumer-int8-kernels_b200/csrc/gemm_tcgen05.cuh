@@ -10,7 +10,7 @@
 //
 // kCtas == 1: one CTA per 128x256 output tile.
 // kCtas == 2: a two-CTA cluster shares a 256x256 tile; each CTA stages its own 128 rows of A
-//             and its own 128 rows of W (plain, non-multicast TMA loads) and the pair leader
+//             and its own 128 rows of W (each CTA issues its own plain TMA loads) and the pair leader
 //             issues tcgen05.mma.cta_group::2, which reads both CTAs' shared memory.
 // Modes:
 //   kModeFused      signed INT8 weights, BF16 output only (fused_channel_mm)

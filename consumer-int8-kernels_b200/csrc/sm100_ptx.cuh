@@ -108,7 +108,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
-// ---------------------------------------------------------------- TMA (no multicast anywhere)
+// ---------------------------------------------------------------- TMA (every load is issued per CTA)
 __device__ __forceinline__ void prefetch_tensormap(const void* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
