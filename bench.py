@@ -197,10 +197,12 @@ def run_ours(args, spec, rank, world, local_rank):
     gen = torch.Generator().manual_seed(0)
     x_host = workloads.activations(m, k, gen).pin_memory()
     w, w_scale = workloads.weights(n, k, gen)
-    plan = ShardPlan(m, n, k, world, rank, chunks=args.chunks if world > 1 else 1)
+    fused = args.gather == "fused" and world > 1
+    plan = ShardPlan(m, n, k, world, rank, chunks=args.chunks if world > 1 and not fused else 1)
     w_shard, sw_shard = plan.shard_weights(w, w_scale)
     del w
-    layer = ColumnShardedLinear(plan, w_shard.to(device), sw_shard.to(device), schedule=args.schedule)
+    layer = ColumnShardedLinear(plan, w_shard.to(device), sw_shard.to(device), schedule=args.schedule,
+                                mode="fused" if fused else "nccl")
     x = x_host.to(device)
     out_host = torch.empty(m, plan.shard_n, dtype=torch.bfloat16).pin_memory()
 
@@ -282,7 +284,9 @@ def run_ours(args, spec, rank, world, local_rank):
         warmup=max(args.warmup, 3), ms_per_step=step_ms, higher_is_better=True, scaling="strong", vs_baseline=None,
         dtype="int8", data="synthetic",
         config=dict(workload=f"{args.workload} {spec['config']} M={m} K={k} N={n}", parallelism=f"N-sharded x{world}",
-                    gather="NCCL all-gather of BF16 [M,N/G] blocks" if world > 1 else "none",
+                    gather=("none" if world == 1 else
+                            "fused: GEMM epilogue TMA-stores each tile into every rank's symmetric-memory buffer" if fused
+                            else "NCCL all-gather of BF16 [M,N/G] blocks"),
                     row_chunks=plan.chunks, schedule=args.schedule,
                     l2="inputs larger than L2 (weights+activations+output per step exceed 126 MB); no flush"),
         roofline=dict(bound="tensor", achieved=gemm_tops, peak=tensor_peak, unit="TFLOP/s", frac=gemm_tops / tensor_peak,
@@ -430,7 +434,10 @@ def main():
     parser.add_argument("--profile-only", action="store_true",
                         help="run --steps launches of the workload's kernels with no timing (for ncu captures)")
     parser.add_argument("--schedule", type=int, default=0)
-    parser.add_argument("--chunks", type=int, default=4, help="row chunks whose gather overlaps the next GEMM (N>1)")
+    parser.add_argument("--gather", choices=["fused", "nccl"], default="fused",
+                        help="N>1: peer stores from the GEMM epilogue, or a separate NCCL all-gather")
+    parser.add_argument("--chunks", type=int, default=4,
+                        help="--gather nccl: row chunks whose gather overlaps the next GEMM")
     parser.add_argument("--no-extra", action="store_true", help="skip the other benchmark configs")
     args = parser.parse_args()
     spec = WORKLOADS[args.workload]

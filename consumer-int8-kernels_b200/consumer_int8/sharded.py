@@ -4,8 +4,14 @@ The reference has no collective of its own; its serving stack runs these project
 parallel and gathers the result (benchmarks/microbench.py:187 "column parallel + gather").
 Here rank r owns ``w[r*N/G:(r+1)*N/G]`` and its channel scales, the activations are replicated,
 every rank quantizes them itself (cheap next to the GEMM) and computes a BF16 ``[M, N/G]`` column
-block, and one NCCL all-gather of that BF16 block — nothing else crosses NVLink — leaves the
-whole output on every rank.
+block; only that BF16 block crosses NVLink, and afterwards the whole output is on every rank.
+Two ways to move it:
+
+* ``mode="fused"`` (default on CUDA): the gathered buffers live in symmetric memory, every rank
+  maps its peers' buffers, and the GEMM's epilogue stores each finished tile into block ``rank`` of
+  every rank's buffer (``ops.fused_channel_mm_gather``), so the transfers overlap the main loop and
+  no communication kernel competes with the persistent GEMM for SMs. A barrier ends the call.
+* ``mode="nccl"``: the GEMM writes its block locally and one NCCL all-gather moves it.
 
 Layout of the gathered output: ``[chunks, G, M/chunks, N/G]``. Column blocks of a row-major
 ``[M, N]`` matrix are not contiguous, so each rank's block is kept contiguous instead and the
@@ -85,7 +91,8 @@ class ColumnShardedLinear:
     """
 
     def __init__(self, plan: ShardPlan, w_shard: torch.Tensor, w_scale_shard: torch.Tensor,
-                 group: dist.ProcessGroup | None = None, schedule: int = 0, operators=None):
+                 group: dist.ProcessGroup | None = None, schedule: int = 0, operators=None,
+                 mode: str = "nccl"):
         if operators is None:
             from . import ops as operators  # the compiled operators; there is no fallback
 
@@ -100,7 +107,25 @@ class ColumnShardedLinear:
         device = w_shard.device
         self.codes = torch.empty(plan.m, plan.k, dtype=torch.int8, device=device)
         self.scales = torch.empty(plan.m, dtype=torch.float32, device=device)
-        self.gathered = torch.empty(plan.gathered_shape, dtype=torch.bfloat16, device=device)
+        if mode not in ("nccl", "fused"):
+            raise ValueError("mode must be 'nccl' or 'fused'")
+        self.mode = mode if plan.world > 1 else "nccl"
+        self.peer_ptrs = None
+        if self.mode == "fused":
+            if plan.chunks != 1:
+                raise ValueError("the fused gather overlaps tile by tile; use chunks=1")
+            if plan.shard_n % 8:
+                raise ValueError("the fused gather needs N/G % 8 == 0")
+            import torch.distributed._symmetric_memory as symm_mem
+
+            flat = symm_mem.empty(plan.world * plan.m * plan.shard_n, dtype=torch.bfloat16, device=device)
+            handle = symm_mem.rendezvous(flat, group=group if group is not None else dist.group.WORLD)
+            self._symm_handle = handle          # keeps the peer mappings alive
+            self.peer_ptrs = torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64)
+            self.gathered = flat.view(plan.gathered_shape)
+            self._barrier_word = torch.zeros(1, dtype=torch.float32, device=device)
+        else:
+            self.gathered = torch.empty(plan.gathered_shape, dtype=torch.bfloat16, device=device)
         overlap = plan.chunks > 1 and plan.world > 1 and device.type == "cuda"
         self.comm_stream = torch.cuda.Stream(device=device) if overlap else None
         self._chunk_done = [torch.cuda.Event() for _ in range(plan.chunks)] if self.comm_stream else []
@@ -123,6 +148,14 @@ class ColumnShardedLinear:
             self.compute(x)
             return self.gathered
         self.ops.quantize_rows(x, self.codes, self.scales)
+        if self.mode == "fused":
+            # every rank writes its block into every rank's buffer; the barrier orders those peer
+            # writes before any rank reads. A rank must not start its next forward while a peer is
+            # still reading the previous result (alternate two layers, or barrier before the call).
+            self.ops.fused_channel_mm_gather(self.codes, self.w, self.scales, self.w_scale,
+                                             self.gathered[0], self.peer_ptrs, plan.rank, self.schedule)
+            dist.all_reduce(self._barrier_word, group=self.group)   # stream-ordered, no host sync
+            return self.gathered
         main = torch.cuda.current_stream() if self.comm_stream is not None else None
         for c in range(plan.chunks):
             rows = slice(c * plan.chunk_m, (c + 1) * plan.chunk_m)

@@ -188,6 +188,45 @@ void boxed_grouped_mm(StableIValue* stack, uint64_t, uint64_t) {
                                   static_cast<float*>(scales.data_ptr()), sw.data_ptr(), out.data_ptr(), m, n,
                                   groups, stream_for(device)));
 }
+
+// Additive operator: this rank's output-channel shard of fused_channel_mm, written straight into
+// block `rank` of every rank's gathered buffer [world, M, N/world] (peer-mapped symmetric memory).
+// peer_ptrs is a CPU INT64 tensor holding the device address of every rank's buffer.
+void boxed_fused_mm_gather(StableIValue* stack, uint64_t, uint64_t) {
+  auto a = to<Tensor>(stack[0]), w = to<Tensor>(stack[1]);
+  auto sa = to<Tensor>(stack[2]), sw = to<Tensor>(stack[3]);
+  auto gathered = to<Tensor>(stack[4]), peer_ptrs = to<Tensor>(stack[5]);
+  const int64_t rank = to<int64_t>(stack[6]), schedule = to<int64_t>(stack[7]);
+  const int device = a.get_device_index();
+  check(a, ScalarType::Char, device);
+  check(w, ScalarType::Char, device);
+  check(sa, ScalarType::Float, device);
+  check(sw, ScalarType::BFloat16, device);
+  check(gathered, ScalarType::BFloat16, device);
+  STD_TORCH_CHECK(!peer_ptrs.is_cuda() && peer_ptrs.is_contiguous() && peer_ptrs.scalar_type() == ScalarType::Long &&
+                      peer_ptrs.dim() == 1,
+                  "peer_ptrs must be a contiguous CPU INT64 vector");
+  STD_TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && gathered.dim() == 3, "Expected matrices and a [world,M,N/world] buffer");
+  const int64_t m = a.size(0), n = w.size(0), k = a.size(1), world = peer_ptrs.size(0);
+  STD_TORCH_CHECK(m > 0 && n > 0 && k > 0 && n % 8 == 0 && k % 32 == 0 && k <= 65536 && w.size(1) == k &&
+                      world > 0 && world <= 8 && rank >= 0 && rank < world && gathered.size(0) == world &&
+                      gathered.size(1) == m && gathered.size(2) == n && sa.dim() == 1 && sw.dim() == 1 &&
+                      sa.size(0) == m && sw.size(0) == n,
+                  "Invalid sharded GEMM geometry");
+  STD_TORCH_CHECK(a.numel() <= kIntMax && w.numel() <= kIntMax && gathered.numel() <= kIntMax, "Matrix too large");
+  STD_TORCH_CHECK(schedule >= 0 && schedule <= 6, "Invalid fused GEMM schedule");
+  const int64_t* addresses = static_cast<const int64_t*>(peer_ptrs.data_ptr());
+  STD_TORCH_CHECK(static_cast<uintptr_t>(addresses[rank]) == address(gathered),
+                  "peer_ptrs[rank] must be the address of this rank's gathered buffer");
+  void* buffers[8];
+  for (int64_t r = 0; r < world; ++r) buffers[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(addresses[r]));
+  STD_TORCH_CHECK(address(a) % 16 == 0 && address(w) % 16 == 0, "Matrix operands must be 16-byte aligned");
+  torch::stable::accelerator::DeviceGuard guard(device);
+  launched(ci8_fused_channel_mm_gather(static_cast<int8_t*>(a.data_ptr()), static_cast<int8_t*>(w.data_ptr()),
+                                       static_cast<float*>(sa.data_ptr()), sw.data_ptr(), buffers,
+                                       static_cast<int>(world), static_cast<int>(rank), m, n, k,
+                                       static_cast<int>(schedule), stream_for(device)));
+}
 }  // namespace
 
 STABLE_TORCH_LIBRARY(consumer_int8, m) {
@@ -198,6 +237,7 @@ STABLE_TORCH_LIBRARY(consumer_int8, m) {
   m.def("channel_gemv(Tensor x, Tensor w, Tensor scale, Tensor(a!) out) -> ()");
   m.def("cutlass_channel_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) workspace, Tensor(b!) out) -> ()");
   m.def("grouped_channel_mm(Tensor codes, Tensor w, Tensor scales, Tensor w_scale, Tensor(a!) out) -> ()");
+  m.def("fused_channel_mm_gather(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) gathered, Tensor peer_ptrs, int rank, int schedule=0) -> ()");
 }
 STABLE_TORCH_LIBRARY_IMPL(consumer_int8, CUDA, m) {
   m.impl("fused_channel_mm", &boxed_fused_mm);
@@ -207,6 +247,7 @@ STABLE_TORCH_LIBRARY_IMPL(consumer_int8, CUDA, m) {
   m.impl("channel_gemv", &boxed_gemv);
   m.impl("cutlass_channel_mm", &boxed_cutlass_mm);
   m.impl("grouped_channel_mm", &boxed_grouped_mm);
+  m.impl("fused_channel_mm_gather", &boxed_fused_mm_gather);
 }
 extern "C" PyObject* PyInit__C() {
   static PyModuleDef module = {PyModuleDef_HEAD_INIT, "_C", nullptr, -1, nullptr};

@@ -89,8 +89,26 @@ cudaError_t make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
 bool aligned(const void* p, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(p) % bytes == 0; }
 
 // ------------------------------------------------------------------ tcgen05 GEMM launch
+// BF16 [rows, cols] output matrix -> store boxes of 64 columns x 32 rows with the 128-byte swizzle.
+cudaError_t make_output_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols) {
+  EncodeTiled encode = encode_tiled_fn();
+  if (!encode) return cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64u, 32u};
+  const cuuint32_t elem[2] = {1u, 1u};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box,
+                            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+// `outputs` lists every destination of the BF16 result (this GPU's buffer and, for the gathering
+// form, the matching block in each peer's buffer). When the row pitch allows it they are written
+// with TMA tile stores; otherwise the single local output takes the direct-store path.
 template <int kCtas, int kMode>
-cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cudaStream_t stream) {
+cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cudaStream_t stream,
+                        void* const* outputs = nullptr, int num_outputs = 0) {
   using Cfg = GemmConfig<kCtas, kMode>;
   static std::atomic<uint64_t> smem_done{0};
   auto kernel = gemm_i8_kernel<kCtas, kMode>;
@@ -110,6 +128,24 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   if (err != cudaSuccess) return err;
   err = make_map(&map_w, w, p.n, static_cast<uint64_t>(p.k) * p.groups, Cfg::kBRowsLoad);
   if (err != cudaSuccess) return err;
+  OutputMaps out_maps = {};
+  void* local_only[1] = {p.out};
+  if (!outputs) {
+    outputs = local_only;
+    num_outputs = 1;
+  }
+  bool tile_stores = kMode != kModeBiased && p.n % 8 == 0 && num_outputs <= kMaxOutputs;
+  for (int d = 0; d < num_outputs; ++d) tile_stores = tile_stores && aligned(outputs[d], 16);
+  p.num_outputs = 0;
+  if (tile_stores) {
+    for (int d = 0; d < num_outputs; ++d) {
+      err = make_output_map(&out_maps.map[d], outputs[d], p.m, p.n);
+      if (err != cudaSuccess) return err;
+    }
+    p.num_outputs = num_outputs;
+  } else if (num_outputs != 1) {
+    return cudaErrorInvalidValue;   // several destinations need the tile-store path
+  }
 
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   const int sms = sm_count();
@@ -130,7 +166,7 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   config.blockDim = dim3(Cfg::kThreads);
   config.dynamicSmemBytes = Cfg::kSmemBytes;
   config.stream = stream;
-  return cudaLaunchKernelEx(&config, kernel, map_a, map_w, p);
+  return cudaLaunchKernelEx(&config, kernel, map_a, map_w, out_maps, p);
 }
 
 // ------------------------------------------------------------------ decode (M <= 16) launch
@@ -314,7 +350,7 @@ int ci8_fused_channel_mm(const int8_t* a, const int8_t* w, const float* a_scale,
     return launch_decode<false>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, k, 1, 0, 0, 0};
+               m, n, k, 1, 0, 0, 0, 0};
   // schedule 0: pairs of CTAs once there is more than one 128-row block; odd values force the
   // single-CTA tile, even values the two-CTA tile. All give identical bits.
   const bool pair = schedule == 0 ? m > 128 : (schedule % 2 == 0);
@@ -333,7 +369,7 @@ int ci8_cutlass_channel_mm(const int8_t* a, const int8_t* w, const float* a_scal
     return launch_decode<false>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), workspace,
-               m, n, k, 1, 0, 0, 0};
+               m, n, k, 1, 0, 0, 0, 0};
   return m > 128 ? launch_gemm<2, kModeWorkspace>(a, w, p, s) : launch_gemm<1, kModeWorkspace>(a, w, p, s);
 }
 
@@ -348,7 +384,7 @@ int ci8_channel_mm(const int8_t* a, const uint8_t* w, const float* a_scale, cons
     return launch_decode<true>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, k, 1, 0, 0, 0};
+               m, n, k, 1, 0, 0, 0, 0};
   return launch_gemm<1, kModeBiased>(a, w, p, s);
 }
 
@@ -372,9 +408,33 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
       static_cast<long long>(m) * n > INT32_MAX || !aligned(codes, 16) || !aligned(w, 16))
     return kInvalid;
   GemmParams p{scales, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, 4096, groups, 0, 0, 0};
+               m, n, 4096, groups, 0, 0, 0, 0};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return m > 128 ? launch_gemm<2, kModeGrouped>(codes, w, p, s) : launch_gemm<1, kModeGrouped>(codes, w, p, s);
+}
+
+int ci8_fused_channel_mm_gather(const int8_t* a, const int8_t* w, const float* a_scale, const void* w_scale,
+                                void* const* gathered, int world, int rank, int m, int n_shard, int k,
+                                int schedule, ci8_stream_t stream) {
+  if (!a || !w || !a_scale || !w_scale || !gathered || world <= 0 || world > kMaxOutputs || rank < 0 ||
+      rank >= world || !gemm_geometry_ok(m, n_shard, k) || n_shard % 8 != 0 || schedule < 0 || schedule > 6 ||
+      !aligned(a, 16) || !aligned(w, 16) || static_cast<long long>(m) * n_shard * world > INT32_MAX)
+    return kInvalid;
+  // destination d = the [m, n_shard] block number `rank` of peer (rank + d) % world: every rank starts
+  // with its own buffer and walks the peers in a different order, which spreads the NVLink traffic
+  void* outputs[kMaxOutputs];
+  const size_t block_bytes = static_cast<size_t>(m) * n_shard * 2;
+  for (int d = 0; d < world; ++d) {
+    void* base = gathered[(rank + d) % world];
+    if (!base || !aligned(base, 16)) return kInvalid;
+    outputs[d] = static_cast<char*>(base) + block_bytes * rank;
+  }
+  GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(outputs[0]), nullptr,
+               m, n_shard, k, 1, 0, 0, 0, 0};
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const bool pair = schedule == 0 ? m > 128 : (schedule % 2 == 0);
+  return pair ? launch_gemm<2, kModeFused>(a, w, p, s, outputs, world)
+              : launch_gemm<1, kModeFused>(a, w, p, s, outputs, world);
 }
 
 // Test hook: the decode kernel with a forced split-K factor (1, 2 or 4); weights_biased != 0

@@ -6,12 +6,17 @@
 //   warp 1      tcgen05.mma kind::i8 issuer (one elected lane), accumulators in TMEM,
 //               two 256-column accumulator buffers so a tile's epilogue overlaps the next
 //               tile's main loop; also owns the TMEM allocation
-//   warps 2..   epilogue: tcgen05.ld -> FP32 row scale -> FP32 channel scale -> BF16 stores
+//   warps 2..   epilogue: tcgen05.ld -> FP32 row scale -> FP32 channel scale -> BF16, staged
+//               through a small swizzled shared-memory buffer and written with TMA tile stores
+//               (full 128-byte lines; the same tile can be stored to several destinations, which
+//               is how the N-sharded form writes its column block into every peer GPU's gathered
+//               output while the main loop keeps running). Outputs whose row pitch is not a
+//               multiple of 16 bytes take a direct-store path instead.
 //
 // kCtas == 1: one CTA per 128x256 output tile.
 // kCtas == 2: a two-CTA cluster shares a 256x256 tile; each CTA stages its own 128 rows of A
-//             and its own 128 rows of W (each CTA issues its own plain TMA loads) and the pair leader
-//             issues tcgen05.mma.cta_group::2, which reads both CTAs' shared memory.
+//             and its own 128 rows of W (each CTA issues its own plain TMA loads) and the pair
+//             leader issues tcgen05.mma.cta_group::2, which reads both CTAs' shared memory.
 // Modes:
 //   kModeFused      signed INT8 weights, BF16 output only (fused_channel_mm)
 //   kModeWorkspace  as fused, and the INT32 accumulators are also written to a caller buffer
@@ -32,15 +37,23 @@ namespace ci8 {
 
 enum GemmMode { kModeFused = 0, kModeWorkspace = 1, kModeBiased = 2, kModeGrouped = 3 };
 
+constexpr int kMaxOutputs = 8;   // destinations of one output tile (this GPU + up to 7 peers)
+
 struct GemmParams {
   const float* sa;            // [M] (grouped: [G,M])
   const __nv_bfloat16* sw;    // [N]
-  __nv_bfloat16* out;         // [M,N]
+  __nv_bfloat16* out;         // [M,N] (direct-store path)
   int32_t* workspace;         // [M,N] or nullptr
   int m, n, k;                // k = K per group
   int groups;                 // 1 unless grouped
   int tiles_m, tiles_n;
   int group_m;                // row tiles per raster group (L2 reuse of the A rows)
+  int num_outputs;            // TMA-store destinations in OutputMaps; 0 selects direct stores
+};
+
+// Tensor maps of the output destinations: BF16 [M,N] matrices, boxes of 64 columns x 32 rows.
+struct OutputMaps {
+  CUtensorMap map[kMaxOutputs];
 };
 
 template <int kCtas, int kMode>
@@ -60,9 +73,13 @@ struct GemmConfig {
   static constexpr int kEpiWarps = kMode == kModeGrouped ? 8 : 4;
   static constexpr int kThreads = (2 + kEpiWarps) * 32;
   static constexpr int kColsPerEpiWarp = kTileN / (kEpiWarps / 4);
+  static constexpr int kStoreBoxBytes = 32 * 128;     // one staged store box: 32 rows x 64 BF16
+  static constexpr int kStoreBufs = kEpiWarps == 4 ? 2 : 1;   // staging boxes per epilogue warp
+  static constexpr int kStagingBytes = kEpiWarps * kStoreBufs * kStoreBoxBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + align slack
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
   static_assert(kMode != kModeBiased || kCtas == 1, "biased weights use the single-CTA tile");
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
 // Tile order: row tiles are walked in groups of group_m; inside a group the row tile index runs
@@ -86,15 +103,18 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 template <int kCtas, int kMode>
 __global__ void __launch_bounds__(GemmConfig<kCtas, kMode>::kThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
-               const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+               const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ OutputMaps out_maps, const GemmParams p) {
   using Cfg = GemmConfig<kCtas, kMode>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
   const uint32_t smem_base = raw_addr + pad;
-  uint8_t* bar_region = smem + Cfg::kStages * Cfg::kStageBytes;
-  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  constexpr int kRingBytes = Cfg::kStages * Cfg::kStageBytes;
+  uint8_t* staging = smem + kRingBytes;
+  uint8_t* bar_region = staging + Cfg::kStagingBytes;
+  const uint32_t bar_base = smem_base + kRingBytes + Cfg::kStagingBytes;
   // barrier layout (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
@@ -122,6 +142,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_w);
+    for (int d = 0; d < p.num_outputs; ++d) prefetch_tensormap(&out_maps.map[d]);
   }
   if constexpr (kMode == kModeBiased) {
     // Sixteen rows of ones behind the 240 weight rows of every stage (the swizzle permutes
@@ -232,17 +253,19 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     const int epi = warp - 2;
     const int quarter = warp & 3;                       // TMEM lanes this warp may read
     const int col_base = (epi >> 2) * Cfg::kColsPerEpiWarp;
-    constexpr int kChunks = Cfg::kColsPerEpiWarp / 32;
-    const uint32_t leader_empty0 = kCtas == 2 ? map_to_cta(tmem_empty_bar(0), 0) : tmem_empty_bar(0);
+    constexpr int kChunks = Cfg::kColsPerEpiWarp / 64;  // 64 output columns per staged box
+    const bool tma_out = p.num_outputs > 0;
     const bool out_vec = (p.n % 8 == 0) && (reinterpret_cast<uintptr_t>(p.out) % 16 == 0);
     const bool ws_vec = (p.n % 4 == 0) && (reinterpret_cast<uintptr_t>(p.workspace) % 16 == 0);
-    uint32_t acc_iter = 0;
+    uint8_t* my_staging = staging + epi * Cfg::kStoreBufs * Cfg::kStoreBoxBytes;
+    uint32_t acc_iter = 0, store_iter = 0;
     bool ok = true;
     float total[kMode == kModeGrouped ? Cfg::kColsPerEpiWarp : 1];
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
       int mt, nt;
       tile_coords(p, tile, mt, nt);
-      const int row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM + quarter * 32 + lane;
+      const int row0 = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM + quarter * 32;
+      const int row = row0 + lane;
       const int n0 = nt * Cfg::kChannelsPerTile;
       for (int g = 0; g < p.groups; ++g, ++acc_iter) {
         const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
@@ -259,73 +282,104 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
           tmem_ld_wait();
           bias = static_cast<int32_t>(ones[0]) * 128;
         }
+        const bool last_group = g + 1 == p.groups;
 #pragma unroll
         for (int chunk = 0; chunk < kChunks; ++chunk) {
-          const int c0 = n0 + col_base + chunk * 32;
-          if (kMode == kModeBiased && col_base + chunk * 32 >= Cfg::kChannelsPerTile) break;
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + chunk * 32, v);
-          tmem_ld_wait();
-          if constexpr (kMode == kModeGrouped) {
+          const int c0 = n0 + col_base + chunk * 64;      // first output column of this 64-wide box
+          const bool store_box = (kMode != kModeGrouped || last_group) && c0 < p.n;
+          uint8_t* box = my_staging + (store_iter % Cfg::kStoreBufs) * Cfg::kStoreBoxBytes;
+          if (tma_out && store_box && store_iter >= Cfg::kStoreBufs) {
+            // the box is reused only after its previous stores have finished reading it
+            if (lane == 0) tma_store_wait_read<Cfg::kStoreBufs - 1>();
+            __syncwarp();
+          }
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float term = __fmul_rn(__int2float_rn(static_cast<int32_t>(v[j])), row_scale);
-              total[chunk * 32 + j] = g == 0 ? term : __fadd_rn(total[chunk * 32 + j], term);
+          for (int half = 0; half < 2; ++half) {
+            const int h0 = c0 + half * 32;                // 32 columns per TMEM load
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + chunk * 64 + half * 32, v);
+            tmem_ld_wait();
+            if constexpr (kMode == kModeGrouped) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float term = __fmul_rn(__int2float_rn(static_cast<int32_t>(v[j])), row_scale);
+                const int t = chunk * 64 + half * 32 + j;
+                total[t] = g == 0 ? term : __fadd_rn(total[t], term);
+              }
             }
-            if (g + 1 < p.groups) continue;
-          }
-          if (c0 >= p.n) continue;
-          // channel scales for this chunk: lane j holds sw[c0 + j]
-          const float my_sw = (c0 + lane < p.n) ? __bfloat162float(p.sw[c0 + lane]) : 0.f;
-          const int limit = kMode == kModeBiased
-                                ? min(p.n - c0, Cfg::kChannelsPerTile - (col_base + chunk * 32))
-                                : p.n - c0;
-          if constexpr (kMode == kModeBiased || kMode == kModeWorkspace) {
+            if (!store_box || h0 >= p.n) continue;
+            // channel scales of these 32 columns: lane j holds sw[h0 + j]
+            const float my_sw = (h0 + lane < p.n) ? __bfloat162float(p.sw[h0 + lane]) : 0.f;
+            const int limit = kMode == kModeBiased
+                                  ? min(p.n - h0, Cfg::kChannelsPerTile - (col_base + chunk * 64 + half * 32))
+                                  : p.n - h0;
+            if constexpr (kMode == kModeBiased) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = static_cast<uint32_t>(static_cast<int32_t>(v[j]) - bias);
-          }
-          if constexpr (kMode == kModeWorkspace) {
-            if (row < p.m) {
-              int32_t* ws = p.workspace + static_cast<size_t>(row) * p.n + c0;
-              if (ws_vec && limit >= 32) {
+              for (int j = 0; j < 32; ++j) v[j] = static_cast<uint32_t>(static_cast<int32_t>(v[j]) - bias);
+            }
+            if constexpr (kMode == kModeWorkspace) {
+              if (row < p.m) {
+                int32_t* ws = p.workspace + static_cast<size_t>(row) * p.n + h0;
+                if (ws_vec && limit >= 32) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                  *reinterpret_cast<uint4*>(ws + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                  for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<uint4*>(ws + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                } else {
+                  for (int j = 0; j < 32; ++j)
+                    if (j < limit) ws[j] = static_cast<int32_t>(v[j]);
+                }
+              }
+            }
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float s0 = __shfl_sync(0xffffffffu, my_sw, j);
+              const float s1 = __shfl_sync(0xffffffffu, my_sw, j + 1);
+              float f0, f1;
+              if constexpr (kMode == kModeGrouped) {
+                f0 = total[chunk * 64 + half * 32 + j];
+                f1 = total[chunk * 64 + half * 32 + j + 1];
+              } else {
+                f0 = __fmul_rn(__int2float_rn(static_cast<int32_t>(v[j])), row_scale);
+                f1 = __fmul_rn(__int2float_rn(static_cast<int32_t>(v[j + 1])), row_scale);
+              }
+              packed[j >> 1] = pack_bf16x2(__fmul_rn(f0, s0), __fmul_rn(f1, s1));
+            }
+            if (tma_out) {
+              // Stage with the 128-byte swizzle the store's tensor map expects: 16-byte chunk c of
+              // box row r lives at chunk c ^ (r & 7).
+              uint4* row_base = reinterpret_cast<uint4*>(box + lane * 128);
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+                row_base[(half * 4 + c) ^ (lane & 7)] =
+                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            } else if (row < p.m) {
+              __nv_bfloat16* dst = p.out + static_cast<size_t>(row) * p.n + h0;
+              if (out_vec && limit >= 32) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 4)
+                  *reinterpret_cast<uint4*>(dst + 2 * j) =
+                      make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
               } else {
                 for (int j = 0; j < 32; ++j)
-                  if (j < limit) ws[j] = static_cast<int32_t>(v[j]);
+                  if (j < limit) {
+                    const uint32_t word = packed[j >> 1];
+                    reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>((j & 1) ? (word >> 16) : (word & 0xffffu));
+                  }
               }
             }
           }
-          uint32_t packed[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float s0 = __shfl_sync(0xffffffffu, my_sw, j);
-            const float s1 = __shfl_sync(0xffffffffu, my_sw, j + 1);
-            float f0, f1;
-            if constexpr (kMode == kModeGrouped) {
-              f0 = total[chunk * 32 + j];
-              f1 = total[chunk * 32 + j + 1];
-            } else {
-              f0 = __fmul_rn(__int2float_rn(static_cast<int32_t>(v[j])), row_scale);
-              f1 = __fmul_rn(__int2float_rn(static_cast<int32_t>(v[j + 1])), row_scale);
+          if (tma_out && store_box) {
+            // one lane stores the staged box to every destination (columns past N and rows past M
+            // are clipped by the tensor map)
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && row0 < p.m) {
+              for (int d = 0; d < p.num_outputs; ++d)
+                tma_store_2d(&out_maps.map[d], smem_u32(box), c0, row0);
+              tma_store_commit();
             }
-            packed[j >> 1] = pack_bf16x2(__fmul_rn(f0, s0), __fmul_rn(f1, s1));
-          }
-          if (row < p.m) {
-            __nv_bfloat16* dst = p.out + static_cast<size_t>(row) * p.n + c0;
-            if (out_vec && limit >= 32) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 4)
-                *reinterpret_cast<uint4*>(dst + 2 * j) =
-                    make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (j < limit) {
-                  const uint32_t word = packed[j >> 1];
-                  reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>((j & 1) ? (word >> 16) : (word & 0xffffu));
-                }
-            }
+            ++store_iter;
           }
         }
         // this warp is done with the accumulator buffer
@@ -333,10 +387,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
         __syncwarp();
         if (lane == 0) {
           if constexpr (kCtas == 2) mbar_arrive_cluster(tmem_empty_bar(buf), 0);
-          else mbar_arrive(leader_empty0 + 8u * buf);
+          else mbar_arrive(tmem_empty_bar(buf));
         }
       }
     }
+    if (tma_out && lane == 0) tma_store_wait_read<0>();   // staged boxes must outlive their stores
   }
 
   // ------------------------------------------------------------------ teardown

@@ -132,6 +132,23 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* map, 
       : "memory");
 }
 
+// 2-D tile store, shared memory -> global (this GPU's memory or a peer's), tracked by the
+// issuing thread's bulk async-group. Elements outside the tensor are not written.
+__device__ __forceinline__ void tma_store_2d(const void* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Waits until at most kPending of this thread's store groups still have to read shared memory.
+template <int kPending>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+
 // ---------------------------------------------------------------- cluster
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

@@ -74,6 +74,19 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
                            const void* w_scale, void* out, int m, int n, int groups,
                            ci8_stream_t stream);
 
+/* fused_channel_mm for an output-channel shard, with the all-gather of the result fused into the
+ * GEMM's epilogue. The reference has no collective (its serving stack gathers column-parallel
+ * results outside the library, benchmarks/microbench.py:187); this entry point replaces
+ * "fused_channel_mm then all-gather". gathered[r] (r = 0..world-1, a HOST array of device
+ * pointers) is rank r's BF16 buffer [world, m, n_shard], peer-mapped into this process; this
+ * rank's [m, n_shard] result is written into block `rank` of every one of them with TMA tile
+ * stores issued as each tile finishes, so the NVLink transfers overlap the main loop. The caller
+ * must order a cross-rank barrier after this call before any rank reads its buffer.
+ * w INT8 [n_shard, k] is this rank's slice of the weight; n_shard % 8 == 0; world <= 8. */
+int ci8_fused_channel_mm_gather(const int8_t* a, const int8_t* w, const float* a_scale,
+                                const void* w_scale, void* const* gathered, int world, int rank,
+                                int m, int n_shard, int k, int schedule, ci8_stream_t stream);
+
 /* The decode (m <= 16) kernel behind ci8_fused_channel_mm / ci8_cutlass_channel_mm /
  * ci8_channel_mm with the split-K factor forced to 1, 2 or 4 instead of chosen from the shape.
  * No counterpart in the reference; it exists so that tests can show the result does not depend
