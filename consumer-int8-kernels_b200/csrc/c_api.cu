@@ -394,6 +394,16 @@ int ci8_channel_gemv(const void* x, const int8_t* w, const void* w_scale, void* 
       static_cast<long long>(n) * k > INT32_MAX || !aligned(w, 16) || !aligned(x, 4))
     return kInvalid;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (aligned(x, 16)) {
+    // tensor-core path: 64 channels per CTA, K split over four warps
+    const int ctas = (n + kGemvChannelsPerCta - 1) / kGemvChannelsPerCta;
+    const auto* xb = static_cast<const __nv_bfloat16*>(x);
+    const auto* sb = static_cast<const __nv_bfloat16*>(w_scale);
+    auto* ob = static_cast<__nv_bfloat16*>(out);
+    if (m <= 8) gemv_w8a16_mma_kernel<1><<<ctas, 256, 0, s>>>(xb, w, sb, ob, m, n, k);
+    else gemv_w8a16_mma_kernel<2><<<ctas, 256, 0, s>>>(xb, w, sb, ob, m, n, k);
+    return cudaGetLastError();
+  }
   if (m == 1) return launch_gemv<1>(x, w, w_scale, out, m, n, k, s);
   if (m == 2) return launch_gemv<2>(x, w, w_scale, out, m, n, k, s);
   if (m <= 4) return launch_gemv<4>(x, w, w_scale, out, m, n, k, s);

@@ -1,16 +1,169 @@
 // W8A16 small-batch linear: BF16 activations times BF16-rounded dequantized INT8 weights with
 // FP32 accumulation:  wd[n,k] = bf16(float(code[n,k]) * float(sw[n])),
 //                     out[m,n] = bf16(sum_k x[m,k] * wd[n,k]).
-// HBM-bound on the weight stream, which is read exactly once. A warp owns kChannels output
-// channels; each lane reads 16 bytes of weights per 512-wide K step. The activation rows are
-// staged in shared memory in K chunks shared by the whole CTA, so the weight stream is the
-// only global traffic in the inner loop.
+// HBM-bound on the weight stream, which is read exactly once.
+//
+// gemv_w8a16_mma_kernel: the multiply-accumulate runs on the tensor cores with register-fed
+// operands (mma.sync m16n8k16, BF16 x BF16 -> FP32); what is left for the CUDA cores is the
+// dequantisation, 3.75 instructions per weight byte. A warp owns 32 output channels (two 16-row
+// A fragments) and a quarter of K; each lane loads 16 consecutive weight bytes of "its" channel
+// per 64-wide K step. The K index inside a 64-wide step is permuted so that those 16 bytes feed
+// four MMAs directly (the activations are read with the same permutation, so the dot products
+// are unchanged). The four K quarters of a CTA are added through shared memory.
+//
+// gemv_w8a16_kernel: plain FMA version for activations that are not 16-byte aligned.
 #pragma once
 #include <cuda_bf16.h>
 #include <cstdint>
 
 namespace ci8 {
 
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Four INT8 codes (one 32-bit word, already XORed with 0x80808080 so each byte is code+128) ->
+// two BF16 pairs bf16(code * scale): PRMT builds the float 2^23 + (code+128), one FADD removes
+// the offset exactly, one FMUL applies the scale, CVT rounds two values to a BF16 pair.
+__device__ __forceinline__ void dequant4(uint32_t biased, float scale, uint32_t& lo, uint32_t& hi) {
+  constexpr float kOffset = 8388608.f + 128.f;
+  const float c0 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7650)), kOffset);
+  const float c1 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7651)), kOffset);
+  const float c2 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7652)), kOffset);
+  const float c3 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7653)), kOffset);
+  __nv_bfloat162 p0 = __floats2bfloat162_rn(__fmul_rn(c0, scale), __fmul_rn(c1, scale));
+  __nv_bfloat162 p1 = __floats2bfloat162_rn(__fmul_rn(c2, scale), __fmul_rn(c3, scale));
+  lo = *reinterpret_cast<uint32_t*>(&p0);
+  hi = *reinterpret_cast<uint32_t*>(&p1);
+}
+
+constexpr int kGemvKSplit = 4;          // K quarters per CTA
+constexpr int kGemvChannelsPerCta = 64; // two warps of 32 channels
+
+// kRowBlocks = 1 for M <= 8, 2 for M <= 16. x must be 16-byte aligned, k % 16 == 0.
+template <int kRowBlocks>
+__global__ void __launch_bounds__(256)
+gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const int8_t* __restrict__ w,
+                      const __nv_bfloat16* __restrict__ sw, __nv_bfloat16* __restrict__ out,
+                      int m, int n, int k) {
+  __shared__ float partial[kGemvKSplit - 1][2][2][kRowBlocks][32][4];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int channel_block = warp & 1, k_part = warp >> 1;
+  const int c_base = blockIdx.x * kGemvChannelsPerCta + channel_block * 32;
+
+  // K range of this warp in 64-wide steps
+  const int steps = (k + 63) >> 6;
+  const int step_begin = (steps * k_part) / kGemvKSplit;
+  const int step_end = (steps * (k_part + 1)) / kGemvKSplit;
+
+  // channels of this lane's A-fragment rows: group j, rows g and g + 8
+  const int8_t* w_row[2][2];
+  float scale[2][2];
+  bool valid[2][2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int channel = c_base + j * 16 + h * 8 + g;
+      valid[j][h] = channel < n;
+      w_row[j][h] = w + static_cast<size_t>(valid[j][h] ? channel : 0) * k;
+      scale[j][h] = valid[j][h] ? __bfloat162float(sw[channel]) : 0.f;
+    }
+  const __nv_bfloat16* x_row[kRowBlocks];
+  bool x_valid[kRowBlocks];
+#pragma unroll
+  for (int rb = 0; rb < kRowBlocks; ++rb) {
+    x_valid[rb] = rb * 8 + g < m;
+    x_row[rb] = x + static_cast<size_t>(x_valid[rb] ? rb * 8 + g : 0) * k;
+  }
+
+  float acc[2][kRowBlocks][4];
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int rb = 0; rb < kRowBlocks; ++rb)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[j][rb][i] = 0.f;
+
+#pragma unroll 2
+  for (int step = step_begin; step < step_end; ++step) {
+    const int k0 = step * 64 + t * 16;          // this lane's 16 K positions
+    const bool in_k = k0 < k;                   // k % 16 == 0, so a piece is whole or absent
+    uint4 wv[2][2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        wv[j][h] = (in_k && valid[j][h]) ? __ldg(reinterpret_cast<const uint4*>(w_row[j][h] + k0))
+                                         : make_uint4(0u, 0u, 0u, 0u);   // code 0
+    uint4 xv[kRowBlocks][2];
+#pragma unroll
+    for (int rb = 0; rb < kRowBlocks; ++rb) {
+      if (in_k && x_valid[rb]) {
+        const uint4* src = reinterpret_cast<const uint4*>(x_row[rb] + k0);
+        xv[rb][0] = __ldg(src);
+        xv[rb][1] = __ldg(src + 1);
+      } else {
+        xv[rb][0] = xv[rb][1] = make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {   // MMA i consumes weight bytes 4i..4i+3 and activations 4i..4i+3
+      uint32_t b[kRowBlocks][2];
+#pragma unroll
+      for (int rb = 0; rb < kRowBlocks; ++rb) {
+        const uint32_t xw[8] = {xv[rb][0].x, xv[rb][0].y, xv[rb][0].z, xv[rb][0].w,
+                                xv[rb][1].x, xv[rb][1].y, xv[rb][1].z, xv[rb][1].w};
+        b[rb][0] = xw[2 * i];
+        b[rb][1] = xw[2 * i + 1];
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const uint32_t w_lo[4] = {wv[j][0].x, wv[j][0].y, wv[j][0].z, wv[j][0].w};
+        const uint32_t w_hi[4] = {wv[j][1].x, wv[j][1].y, wv[j][1].z, wv[j][1].w};
+        uint32_t a[4];
+        dequant4(w_lo[i] ^ 0x80808080u, scale[j][0], a[0], a[2]);   // row g:   k slots (2t,2t+1), (2t+8,2t+9)
+        dequant4(w_hi[i] ^ 0x80808080u, scale[j][1], a[1], a[3]);   // row g+8
+#pragma unroll
+        for (int rb = 0; rb < kRowBlocks; ++rb) mma_bf16_16816(acc[j][rb], a, b[rb][0], b[rb][1]);
+      }
+    }
+  }
+
+  // add the K quarters: parts 1..3 park their fragments in shared memory, part 0 finishes
+  if (k_part > 0) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int rb = 0; rb < kRowBlocks; ++rb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) partial[k_part - 1][channel_block][j][rb][lane][i] = acc[j][rb][i];
+  }
+  __syncthreads();
+  if (k_part == 0) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int rb = 0; rb < kRowBlocks; ++rb) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float total = acc[j][rb][i];
+#pragma unroll
+          for (int part = 0; part < kGemvKSplit - 1; ++part) total += partial[part][channel_block][j][rb][lane][i];
+          // fragment element i: channel row g (+8 for i >= 2), activation row 2t + (i & 1)
+          const int channel = c_base + j * 16 + (i >> 1) * 8 + g;
+          const int row = rb * 8 + 2 * t + (i & 1);
+          if (channel < n && row < m) out[static_cast<size_t>(row) * n + channel] = __float2bfloat16_rn(total);
+        }
+      }
+  }
+}
+
+// ------------------------------------------------------------------ FMA version (any alignment)
 constexpr int kGemvChunk = 2048;   // K elements of every activation row staged per step
 
 template <int kRows, int kChannels>

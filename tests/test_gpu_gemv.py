@@ -39,3 +39,22 @@ def test_gemv_rejects_unsupported_geometry(ops):
     with pytest.raises(RuntimeError, match="GEMV geometry"):      # k % 16
         ops.channel_gemv(x[:1, :40].contiguous(), w[:, :40].contiguous(), scale,
                          torch.empty(1, 8, dtype=torch.bfloat16, device=DEV))
+
+
+@pytest.mark.parametrize("m,n,k", [(3, 100, 528), (8, 64, 2064)])
+def test_w8a16_with_activations_that_are_only_4_byte_aligned(ops, m, n, k):
+    """The reference only asks for 4-byte aligned activations (csrc/bindings.cpp:303-304); such
+    inputs take the FMA kernel instead of the tensor-core one."""
+    torch.manual_seed(7)
+    storage = torch.randn(m * k + 2, device=DEV, dtype=torch.bfloat16)
+    x = storage[2:].view(m, k)                      # 4 bytes past a 16-byte boundary
+    assert x.data_ptr() % 16 == 4
+    weight = torch.randint(-127, 128, (n, k), device=DEV, dtype=torch.int8)
+    scale = (torch.rand(n, device=DEV) * 0.002).bfloat16()
+    out = torch.empty(m, n, device=DEV, dtype=torch.bfloat16)
+    ops.channel_gemv(x, weight, scale, out)
+    reference = ref.channel_gemv_fp64(x.cpu(), weight.cpu(), scale.cpu())
+    torch.testing.assert_close(out.cpu(), reference, atol=0.004, rtol=0.008)
+    aligned = torch.empty_like(out)
+    ops.channel_gemv(x.clone(), weight, scale, aligned)
+    torch.testing.assert_close(aligned.cpu(), reference, atol=0.004, rtol=0.008)
