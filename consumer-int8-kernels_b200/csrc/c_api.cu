@@ -149,6 +149,20 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
 
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   const int sms = sm_count();
+  // Optional (schedules 3 and 4): the tiles of the last, partial wave are cut into 2 or 4 column
+  // slices so that they spread over the idle CTAs. Off by default: on a power-capped B200 the
+  // partial wave runs at a higher clock and the narrower slices cost more energy per operation,
+  // so the measured gain was nil (not for the biased form: its row-sum column has a fixed place).
+  {
+    const long long workers = kCtas == 2 ? sms / 2 : sms;
+    const long long tail = tiles % workers;
+    int split = 1;
+    if (p.split > 1 && kMode != kModeBiased && tiles > workers && tail > 0 && tail * 2 <= workers)
+      split = tail * 4 <= workers ? 4 : 2;
+    p.split = split;
+    p.full_tiles = static_cast<int>(split > 1 ? tiles - tail : tiles);
+    p.total_items = static_cast<int>(p.full_tiles + (tiles - p.full_tiles) * split);
+  }
   cudaLaunchConfig_t config = {};
   cudaLaunchAttribute attr[1];
   if (kCtas == 2) {
@@ -249,7 +263,23 @@ bool gemm_geometry_ok(int m, int n, int k) {
 template <int kTeam, int kPacks>
 void launch_quantize_vec(const void* x, int8_t* q, float* s, int rows, int k, int m, int groups, cudaStream_t stream) {
   constexpr int kRowsPerCta = 256 / kTeam;
-  quantize_rows_vec_kernel<kTeam, kPacks><<<(rows + kRowsPerCta - 1) / kRowsPerCta, 256, 0, stream>>>(
+  // persistent grid: as many CTAs as fit on the device at once (cached per device), capped by the work
+  static std::atomic<int> resident[kMaxDevices];
+  int device = 0;
+  cudaGetDevice(&device);
+  device = device >= 0 && device < kMaxDevices ? device : 0;
+  int per_device = resident[device].load(std::memory_order_relaxed);
+  if (per_device == 0) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_rows_vec_kernel<kTeam, kPacks>, 256, 0) !=
+            cudaSuccess || per_sm < 1)
+      per_sm = 1;
+    per_device = per_sm * sm_count();
+    resident[device].store(per_device, std::memory_order_relaxed);
+  }
+  const int needed = (rows + kRowsPerCta - 1) / kRowsPerCta;
+  constexpr bool kPersistent = kPacks >= 4 && kPacks <= 9;
+  quantize_rows_vec_kernel<kTeam, kPacks><<<(!kPersistent || needed < per_device) ? needed : per_device, 256, 0, stream>>>(
       static_cast<const uint16_t*>(x), q, s, rows, k, m, groups);
 }
 
@@ -350,10 +380,12 @@ int ci8_fused_channel_mm(const int8_t* a, const int8_t* w, const float* a_scale,
     return launch_decode<false>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, k, 1, 0, 0, 0, 0};
+               m, n, k, 1, 0, 0, 0, 0, 0, 1, 0};
   // schedule 0: pairs of CTAs once there is more than one 128-row block; odd values force the
-  // single-CTA tile, even values the two-CTA tile. All give identical bits.
+  // single-CTA tile, even values the two-CTA tile; 3 and 4 also slice the last wave's tiles.
+  // All give identical bits.
   const bool pair = schedule == 0 ? m > 128 : (schedule % 2 == 0);
+  p.split = (schedule == 3 || schedule == 4) ? 2 : 1;   // > 1 requests last-wave slicing
   return pair ? launch_gemm<2, kModeFused>(a, w, p, s) : launch_gemm<1, kModeFused>(a, w, p, s);
 }
 
@@ -369,7 +401,7 @@ int ci8_cutlass_channel_mm(const int8_t* a, const int8_t* w, const float* a_scal
     return launch_decode<false>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), workspace,
-               m, n, k, 1, 0, 0, 0, 0};
+               m, n, k, 1, 0, 0, 0, 0, 0, 1, 0};
   return m > 128 ? launch_gemm<2, kModeWorkspace>(a, w, p, s) : launch_gemm<1, kModeWorkspace>(a, w, p, s);
 }
 
@@ -384,7 +416,7 @@ int ci8_channel_mm(const int8_t* a, const uint8_t* w, const float* a_scale, cons
     return launch_decode<true>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, k, 1, 0, 0, 0, 0};
+               m, n, k, 1, 0, 0, 0, 0, 0, 1, 0};
   return launch_gemm<1, kModeBiased>(a, w, p, s);
 }
 
@@ -418,7 +450,7 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
       static_cast<long long>(m) * n > INT32_MAX || !aligned(codes, 16) || !aligned(w, 16))
     return kInvalid;
   GemmParams p{scales, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, 4096, groups, 0, 0, 0, 0};
+               m, n, 4096, groups, 0, 0, 0, 0, 0, 1, 0};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return m > 128 ? launch_gemm<2, kModeGrouped>(codes, w, p, s) : launch_gemm<1, kModeGrouped>(codes, w, p, s);
 }
@@ -440,7 +472,7 @@ int ci8_fused_channel_mm_gather(const int8_t* a, const int8_t* w, const float* a
     outputs[d] = static_cast<char*>(base) + block_bytes * rank;
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(outputs[0]), nullptr,
-               m, n_shard, k, 1, 0, 0, 0, 0};
+               m, n_shard, k, 1, 0, 0, 0, 0, 0, 1, 0};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const bool pair = schedule == 0 ? m > 128 : (schedule % 2 == 0);
   return pair ? launch_gemm<2, kModeFused>(a, w, p, s, outputs, world)

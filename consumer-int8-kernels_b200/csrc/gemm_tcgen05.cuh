@@ -49,6 +49,9 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int group_m;                // row tiles per raster group (L2 reuse of the A rows)
   int num_outputs;            // TMA-store destinations in OutputMaps; 0 selects direct stores
+  int full_tiles;             // work items [0, full_tiles) are whole tiles (complete waves)
+  int split;                  // each remaining tile is cut into `split` column slices (1, 2 or 4)
+  int total_items;            // full_tiles + (tiles - full_tiles) * split
 };
 
 // Tensor maps of the output destinations: BF16 [M,N] matrices, boxes of 64 columns x 32 rows.
@@ -85,7 +88,20 @@ struct GemmConfig {
 // Tile order: row tiles are walked in groups of group_m; inside a group the row tile index runs
 // fastest, then the channel tile. One wave of CTAs then touches a bounded set of A rows (which
 // stay in L2 while the weights stream past) instead of every row of a tall A.
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mt, int& nt) {
+// Work items: the tiles of the complete waves are whole; the tiles of the last, partial wave are
+// cut into `split` column slices of 256/split accumulator columns so that they spread over the
+// idle CTAs (item -> tile, first column n_off and width n_width inside the tile).
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int item, int& mt, int& nt, int& n_off,
+                                            int& n_width) {
+  int tile = item;
+  n_off = 0;
+  n_width = 256;
+  if (item >= p.full_tiles) {
+    const int extra = item - p.full_tiles;
+    tile = p.full_tiles + extra / p.split;
+    n_width = 256 / p.split;
+    n_off = (extra % p.split) * n_width;
+  }
   const int per_group = p.group_m * p.tiles_n;
   const int group = tile / per_group;
   const int within = tile - group * per_group;
@@ -169,7 +185,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;   // per group
-  const int total_tiles = p.tiles_m * p.tiles_n;
+  const int total_tiles = p.total_items;   // work items (whole tiles, then column slices)
   const int first_tile = kCtas == 2 ? (blockIdx.x >> 1) : blockIdx.x;
   const int tile_stride = kCtas == 2 ? (gridDim.x >> 1) : gridDim.x;
 
@@ -181,10 +197,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t leader_full0 = kCtas == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
       bool ok = true;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-        int mt, nt;
-        tile_coords(p, tile, mt, nt);
+        int mt, nt, n_off, n_width;
+        tile_coords(p, tile, mt, nt, n_off, n_width);
         const int a_row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM;
-        const int w_row = nt * Cfg::kChannelsPerTile + rank * Cfg::kBRowsSmem;
+        // each CTA of a pair supplies half of the slice's weight rows (the box still loads
+        // kBRowsSmem rows; the MMA reads only the first n_width / kCtas of them)
+        const int w_row = nt * Cfg::kChannelsPerTile + n_off + rank * (n_width / kCtas);
         for (int g = 0; ok && g < p.groups; ++g) {
           for (int kb = 0; kb < num_kb; ++kb) {
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -209,12 +227,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (rank == 0 && lane == 0) {
-      constexpr uint32_t kIdesc =
-          idesc_i8(Cfg::kBlockM * kCtas, Cfg::kTileN, /*b_unsigned=*/kMode == kModeBiased);
       int stage = 0;
       uint32_t phase = 0, acc_iter = 0;
       bool ok = true;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
+        int mt, nt, n_off, n_width;
+        tile_coords(p, tile, mt, nt, n_off, n_width);
+        const uint32_t idesc = idesc_i8(Cfg::kBlockM * kCtas, n_width, /*b_unsigned=*/kMode == kModeBiased);
         for (int g = 0; ok && g < p.groups; ++g, ++acc_iter) {
           const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
           if (!mbar_wait<kCtas == 2>(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -228,7 +247,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint64_t b_desc = smem_desc_sw128(a_addr + Cfg::kABytes);
 #pragma unroll
             for (int ks = 0; ks < Cfg::kBlockK / 32; ++ks)
-              mma_i8<kCtas>(tmem_d, a_desc + 2u * ks, b_desc + 2u * ks, kIdesc,
+              mma_i8<kCtas>(tmem_d, a_desc + 2u * ks, b_desc + 2u * ks, idesc,
                             (kb | ks) != 0 ? 1u : 0u);
             if constexpr (kCtas == 2) {
               mma_commit_pair(map_to_cta(empty_bar(stage), 0));
@@ -262,11 +281,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     bool ok = true;
     float total[kMode == kModeGrouped ? Cfg::kColsPerEpiWarp : 1];
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-      int mt, nt;
-      tile_coords(p, tile, mt, nt);
+      int mt, nt, n_off, n_width;
+      tile_coords(p, tile, mt, nt, n_off, n_width);
       const int row0 = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM + quarter * 32;
       const int row = row0 + lane;
-      const int n0 = nt * Cfg::kChannelsPerTile;
+      const int n0 = nt * Cfg::kChannelsPerTile + n_off;   // first output column of this item
       for (int g = 0; g < p.groups; ++g, ++acc_iter) {
         const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
         if (!mbar_wait<kCtas == 2>(tmem_full_bar(buf), acc_phase, abort_flag)) { ok = false; break; }
@@ -285,6 +304,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
         const bool last_group = g + 1 == p.groups;
 #pragma unroll
         for (int chunk = 0; chunk < kChunks; ++chunk) {
+          if (col_base + chunk * 64 >= n_width) continue;  // a column slice is narrower than the tile
           const int c0 = n0 + col_base + chunk * 64;      // first output column of this 64-wide box
           const bool store_box = (kMode != kModeGrouped || last_group) && c0 < p.n;
           uint8_t* box = my_staging + (store_iter % Cfg::kStoreBufs) * Cfg::kStoreBoxBytes;

@@ -66,63 +66,88 @@ __device__ __forceinline__ uint2 quantize_pack(const uint4& pack, float scale, f
   return make_uint2(quantize_four_exact(pack.x, pack.y, scale), quantize_four_exact(pack.z, pack.w, scale));
 }
 
-// Row addressing shared by the plain and grouped forms. Output row b (0 <= b < rows):
-//   plain   : input row b
-//   grouped : b = g*M + r reads input row r*G + g  (input [M,G,4096], output [G,M,4096])
-__device__ __forceinline__ int64_t input_row_of(int64_t b, int m, int groups) {
-  return groups > 0 ? (b % m) * groups + b / m : b;
+// Rows are walked in INPUT order so that consecutive teams read consecutive memory. Input row i:
+//   plain   : output row i
+//   grouped : i = r*G + g (input [M,G,4096]) writes output row g*M + r (output [G,M,4096])
+__device__ __forceinline__ int64_t output_row_of(int64_t i, int m, int groups) {
+  return groups > 0 ? (i % groups) * static_cast<int64_t>(m) + i / groups : i;
+}
+
+template <int kTeam, int kPacks>
+__device__ __forceinline__ void load_row(uint4 (&pack)[kPacks], const uint16_t* x, int64_t row, int64_t rows,
+                                         int k, int member) {
+  const uint4* src = reinterpret_cast<const uint4*>(x + (row < rows ? row : 0) * k);
+  const int packs_in_row = k >> 3;
+#pragma unroll
+  for (int i = 0; i < kPacks; ++i) {
+    const int index = i * kTeam + member;
+    pack[i] = (row < rows && index < packs_in_row) ? __ldg(src + index) : make_uint4(0, 0, 0, 0);
+  }
 }
 
 // kTeam threads per row (32 or 256), kPacks 16-byte packs per thread; 256 threads per CTA.
+// Rows of up to 3 packs per thread run one team per row with many small CTAs resident (measured
+// faster there); wider rows (4..9 packs) use a persistent grid in which a team strides over the
+// rows and loads its next row before it reduces and converts the current one, so loads stay in
+// flight during the arithmetic. The code is the same: the launch decides the grid.
 // Requires 16-byte aligned rows of x (k % 8 == 0, base aligned) and 8-byte aligned q.
 template <int kTeam, int kPacks>
 __global__ void __launch_bounds__(256)
 quantize_rows_vec_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
                          float* __restrict__ scales, int rows, int k, int m, int groups) {
   constexpr int kRowsPerCta = 256 / kTeam;
-  __shared__ float maxima[8];
+  constexpr bool kPrefetch = kPacks >= 4 && kPacks <= 9;
+  __shared__ float maxima[2][8];
   const int member = threadIdx.x % kTeam;
-  const int64_t out_row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + threadIdx.x / kTeam;
-  const bool active = out_row < rows;
-  const int64_t in_row = active ? input_row_of(out_row, m, groups) : 0;
-  const uint4* src = reinterpret_cast<const uint4*>(x + in_row * k);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kRowsPerCta;
   const int packs_in_row = k >> 3;
+  int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + threadIdx.x / kTeam;
 
   uint4 pack[kPacks];
-  float maximum = 0.f;
+  uint4 next[kPrefetch ? kPacks : 1];
+  load_row<kTeam, kPacks>(pack, x, row, rows, k, member);
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * kRowsPerCta, iter = 0; base < rows;
+       base += stride, row += stride, ++iter) {
+    if constexpr (kPrefetch) load_row<kTeam, kPacks>(next, x, row + stride, rows, k, member);
+    float maximum = 0.f;
 #pragma unroll
-  for (int i = 0; i < kPacks; ++i) {
-    const int index = i * kTeam + member;
-    pack[i] = (active && index < packs_in_row) ? __ldg(src + index) : make_uint4(0, 0, 0, 0);
-  }
+    for (int i = 0; i < kPacks; ++i) {
+      const uint32_t w[4] = {pack[i].x, pack[i].y, pack[i].z, pack[i].w};
 #pragma unroll
-  for (int i = 0; i < kPacks; ++i) {
-    const uint32_t w[4] = {pack[i].x, pack[i].y, pack[i].z, pack[i].w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      maximum = fmaxf(maximum, fabsf(bf16_lo(w[j])));
-      maximum = fmaxf(maximum, fabsf(bf16_hi(w[j])));
+      for (int j = 0; j < 4; ++j) {
+        maximum = fmaxf(maximum, fabsf(bf16_lo(w[j])));
+        maximum = fmaxf(maximum, fabsf(bf16_hi(w[j])));
+      }
     }
-  }
 #pragma unroll
-  for (int mask = 16; mask; mask >>= 1)
-    maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, mask));
-  if constexpr (kTeam == 256) {
-    if ((threadIdx.x & 31) == 0) maxima[threadIdx.x >> 5] = maximum;
-    __syncthreads();
-    maximum = maxima[0];
+    for (int mask = 16; mask; mask >>= 1)
+      maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, mask));
+    if constexpr (kTeam == 256) {
+      float* slot = maxima[iter & 1];      // alternating slots: one barrier per row is enough
+      if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = maximum;
+      __syncthreads();
+      maximum = slot[0];
 #pragma unroll
-    for (int i = 1; i < 8; ++i) maximum = fmaxf(maximum, maxima[i]);
-  }
-  const float scale = fmaxf(__fdiv_rn(maximum, 127.f), 1e-20f);
-  const float inverse = __fdiv_rn(1.f, scale);
-  if (!active) return;
-  if (member == 0) scales[out_row] = scale;
-  uint2* dst = reinterpret_cast<uint2*>(q + out_row * k);
+      for (int i = 1; i < 8; ++i) maximum = fmaxf(maximum, slot[i]);
+    }
+    const float scale = fmaxf(__fdiv_rn(maximum, 127.f), 1e-20f);
+    const float inverse = __fdiv_rn(1.f, scale);
+    if (row < rows) {
+      const int64_t out_row = output_row_of(row, m, groups);
+      if (member == 0) scales[out_row] = scale;
+      uint2* dst = reinterpret_cast<uint2*>(q + out_row * k);
 #pragma unroll
-  for (int i = 0; i < kPacks; ++i) {
-    const int index = i * kTeam + member;
-    if (index < packs_in_row) dst[index] = quantize_pack(pack[i], scale, inverse);
+      for (int i = 0; i < kPacks; ++i) {
+        const int index = i * kTeam + member;
+        if (index < packs_in_row) dst[index] = quantize_pack(pack[i], scale, inverse);
+      }
+    }
+    if constexpr (kPrefetch) {
+#pragma unroll
+      for (int i = 0; i < kPacks; ++i) pack[i] = next[i];
+    } else {
+      load_row<kTeam, kPacks>(pack, x, row + stride, rows, k, member);
+    }
   }
 }
 
