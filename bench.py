@@ -308,7 +308,12 @@ def run_ours(args, spec, rank, world, local_rank):
 
 # DRAM bytes (read + write) per launch of the dominant kernel from the ncu captures summarised
 # under profiles/ (null until a capture of that workload exists).
-KERNEL_TRAFFIC = {}
+KERNEL_TRAFFIC = {
+    # gemm_i8_kernel<2,fused>: dram__bytes_read.sum + dram__bytes_write.sum per launch
+    "sharded": 845.1e6 + 1110.1e6,          # profiles/gemm_i8_kernel_sharded_traffic.md (algorithmic: 1403 MB)
+    "prefill_gate_up": 200.9e6 + 249.3e6,   # profiles/gemm_i8_kernel_prefill_gate_up.md (algorithmic: 484.5 MB)
+    "prefill_down": 435.6e6 + 35.5e6,       # profiles/gemm_i8_kernel_prefill_down.md (algorithmic: 212.8 MB)
+}
 
 
 def _time_graph(fn, launches, replays=5):

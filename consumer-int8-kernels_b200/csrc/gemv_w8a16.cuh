@@ -89,17 +89,24 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const int8_t* __restr
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[j][rb][i] = 0.f;
 
-#pragma unroll 2
-  for (int step = step_begin; step < step_end; ++step) {
-    const int k0 = step * 64 + t * 16;          // this lane's 16 K positions
-    const bool in_k = k0 < k;                   // k % 16 == 0, so a piece is whole or absent
-    uint4 wv[2][2];
+  // weight loads run two steps ahead of the arithmetic (register double buffer)
+  auto load_weights = [&](int step, uint4 (&dst)[2][2]) {
+    const int k0 = step * 64 + t * 16;
+    const bool in_k = step < step_end && k0 < k;   // k % 16 == 0, so a piece is whole or absent
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
       for (int h = 0; h < 2; ++h)
-        wv[j][h] = (in_k && valid[j][h]) ? __ldg(reinterpret_cast<const uint4*>(w_row[j][h] + k0))
-                                         : make_uint4(0u, 0u, 0u, 0u);   // code 0
+        dst[j][h] = (in_k && valid[j][h]) ? __ldg(reinterpret_cast<const uint4*>(w_row[j][h] + k0))
+                                          : make_uint4(0u, 0u, 0u, 0u);   // code 0
+  };
+  uint4 wv[2][2], w_next[2][2], w_next2[2][2];
+  load_weights(step_begin, wv);
+  load_weights(step_begin + 1, w_next);
+  for (int step = step_begin; step < step_end; ++step) {
+    load_weights(step + 2, w_next2);
+    const int k0 = step * 64 + t * 16;          // this lane's 16 K positions
+    const bool in_k = k0 < k;
     uint4 xv[kRowBlocks][2];
 #pragma unroll
     for (int rb = 0; rb < kRowBlocks; ++rb) {
@@ -132,6 +139,13 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const int8_t* __restr
         for (int rb = 0; rb < kRowBlocks; ++rb) mma_bf16_16816(acc[j][rb], a, b[rb][0], b[rb][1]);
       }
     }
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        wv[j][h] = w_next[j][h];
+        w_next[j][h] = w_next2[j][h];
+      }
   }
 
   // add the K quarters: parts 1..3 park their fragments in shared memory, part 0 finishes
