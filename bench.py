@@ -381,6 +381,15 @@ def other_configs(ops, workloads, device, peaks):
         results[name] = dict(gemm_ms=ms, tops=tops, frac_tensor=tops / tensor_peak, frac_nominal_4500=tops / 4500,
                              quantize_us=ms_q * 1e3, quantize_gbs=(3 * m * k + 4 * m) / ms_q / 1e6)
         del wd, x, xs, out, codes
+    # the SwiGLU + quantizer between the two prefill GEMMs: [4096, 2*17408] BF16 -> INT8 [4096, 17408]
+    m, k = 4096, 17408
+    gate_up = [(torch.randn(m, 2 * k, generator=gen) * 3).bfloat16().to(device) for _ in range(2)]
+    codes = torch.empty(m, k, dtype=torch.int8, device=device)
+    scales = torch.empty(m, device=device)
+    ms = _time_graph(lambda i: ops.silu_mul_quantize(gate_up[i % 2], codes, scales), 20)
+    results["silu_mul_quantize_4096x17408"] = dict(us=ms * 1e3, gbs=(5 * m * k + 4 * m) / ms / 1e6,
+                                                   frac_hbm=(5 * m * k + 4 * m) / ms / 1e6 / hbm)
+    del gate_up, codes
     spec = WORKLOADS["grouped"]
     m, n, groups = spec["m"], spec["n"], spec["groups"]
     inputs = workloads.grouped_inputs(m, n, groups, seed=0)

@@ -51,6 +51,38 @@ void boxed_quant(StableIValue* stack, uint64_t, uint64_t) {
                              stream_for(device)));
 }
 
+// silu_mul / silu_mul_quantize: reference csrc/bindings.cpp:32-65 (any width % 8 == 0 is accepted
+// here; the reference takes 8704 and 17408 only).
+void boxed_silu_mul(StableIValue* stack, uint64_t, uint64_t) {
+  auto x = to<Tensor>(stack[0]), out = to<Tensor>(stack[1]);
+  const int device = x.get_device_index();
+  check(x, ScalarType::BFloat16, device);
+  check(out, ScalarType::BFloat16, device);
+  STD_TORCH_CHECK(x.dim() == 2 && out.dim() == 2 && out.size(1) > 0 && out.size(1) % 8 == 0 &&
+                      x.size(1) == 2 * out.size(1) && x.size(0) == out.size(0) && x.numel() <= kIntMax,
+                  "Unsupported SwiGLU shape");
+  STD_TORCH_CHECK(address(x) % 16 == 0 && address(out) % 16 == 0, "SwiGLU requires aligned buffers");
+  torch::stable::accelerator::DeviceGuard guard(device);
+  launched(ci8_silu_mul(x.data_ptr(), out.data_ptr(), x.size(0), out.size(1), stream_for(device)));
+}
+
+void boxed_silu_quant(StableIValue* stack, uint64_t, uint64_t) {
+  auto x = to<Tensor>(stack[0]), codes = to<Tensor>(stack[1]), scales = to<Tensor>(stack[2]);
+  const int device = x.get_device_index();
+  check(x, ScalarType::BFloat16, device);
+  check(codes, ScalarType::Char, device);
+  check(scales, ScalarType::Float, device);
+  STD_TORCH_CHECK(x.dim() == 2 && codes.dim() == 2 && scales.dim() == 1 && codes.size(1) > 0 &&
+                      codes.size(1) % 8 == 0 && codes.size(1) <= 65536 && x.size(1) == 2 * codes.size(1) &&
+                      x.size(0) == codes.size(0) && scales.size(0) == x.size(0) && x.numel() <= kIntMax,
+                  "Unsupported SwiGLU quantization shape");
+  STD_TORCH_CHECK(address(x) % 16 == 0 && address(codes) % 8 == 0, "SwiGLU quantization requires aligned buffers");
+  torch::stable::accelerator::DeviceGuard guard(device);
+  launched(ci8_silu_mul_quantize(x.data_ptr(), static_cast<int8_t*>(codes.data_ptr()),
+                                 static_cast<float*>(scales.data_ptr()), x.size(0), codes.size(1),
+                                 stream_for(device)));
+}
+
 void boxed_grouped_quant(StableIValue* stack, uint64_t, uint64_t) {
   auto x = to<Tensor>(stack[0]), codes = to<Tensor>(stack[1]), scales = to<Tensor>(stack[2]);
   const int device = x.get_device_index();
@@ -230,6 +262,8 @@ void boxed_fused_mm_gather(StableIValue* stack, uint64_t, uint64_t) {
 }  // namespace
 
 STABLE_TORCH_LIBRARY(consumer_int8, m) {
+  m.def("silu_mul(Tensor input, Tensor(a!) out) -> ()");
+  m.def("silu_mul_quantize(Tensor input, Tensor(a!) codes, Tensor(b!) scales) -> ()");
   m.def("fused_channel_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) out, int schedule=0) -> ()");
   m.def("quantize_rows(Tensor input, Tensor(a!) codes, Tensor(b!) scales) -> ()");
   m.def("quantize_grouped4096(Tensor input, Tensor(a!) codes, Tensor(b!) scales) -> ()");
@@ -240,6 +274,8 @@ STABLE_TORCH_LIBRARY(consumer_int8, m) {
   m.def("fused_channel_mm_gather(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) gathered, Tensor peer_ptrs, int rank, int schedule=0) -> ()");
 }
 STABLE_TORCH_LIBRARY_IMPL(consumer_int8, CUDA, m) {
+  m.impl("silu_mul", &boxed_silu_mul);
+  m.impl("silu_mul_quantize", &boxed_silu_quant);
   m.impl("fused_channel_mm", &boxed_fused_mm);
   m.impl("quantize_rows", &boxed_quant);
   m.impl("quantize_grouped4096", &boxed_grouped_quant);

@@ -260,9 +260,10 @@ bool gemm_geometry_ok(int m, int n, int k) {
 }
 
 // ------------------------------------------------------------------ quantizer launch
-template <int kTeam, int kPacks>
+template <int kTeam, int kPacks, bool kSwiGLU = false>
 void launch_quantize_vec(const void* x, int8_t* q, float* s, int rows, int k, int m, int groups, cudaStream_t stream) {
-  constexpr int kRowsPerCta = 256 / kTeam;
+  constexpr int kThreads = kTeam > 256 ? kTeam : 256;
+  constexpr int kRowsPerCta = kThreads / kTeam;
   // persistent grid: as many CTAs as fit on the device at once (cached per device), capped by the work
   static std::atomic<int> resident[kMaxDevices];
   int device = 0;
@@ -271,15 +272,15 @@ void launch_quantize_vec(const void* x, int8_t* q, float* s, int rows, int k, in
   int per_device = resident[device].load(std::memory_order_relaxed);
   if (per_device == 0) {
     int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_rows_vec_kernel<kTeam, kPacks>, 256, 0) !=
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quantize_rows_vec_kernel<kTeam, kPacks, kSwiGLU>, kThreads, 0) !=
             cudaSuccess || per_sm < 1)
       per_sm = 1;
     per_device = per_sm * sm_count();
     resident[device].store(per_device, std::memory_order_relaxed);
   }
   const int needed = (rows + kRowsPerCta - 1) / kRowsPerCta;
-  constexpr bool kPersistent = kPacks >= 4 && kPacks <= 9;
-  quantize_rows_vec_kernel<kTeam, kPacks><<<(!kPersistent || needed < per_device) ? needed : per_device, 256, 0, stream>>>(
+  constexpr bool kPersistent = !kSwiGLU && kPacks >= 4 && kPacks <= 9;
+  quantize_rows_vec_kernel<kTeam, kPacks, kSwiGLU><<<(!kPersistent || needed < per_device) ? needed : per_device, kThreads, 0, stream>>>(
       static_cast<const uint16_t*>(x), q, s, rows, k, m, groups);
 }
 
@@ -315,6 +316,23 @@ cudaError_t launch_quantize(const void* x, int8_t* q, float* s, int rows, int k,
     if (groups > 0) return cudaErrorInvalidValue;   // the grouped form requires aligned buffers
     quantize_rows_generic_kernel<<<rows, 256, 0, stream>>>(static_cast<const uint16_t*>(x), q, s, k);
   }
+  return cudaGetLastError();
+}
+
+// silu_mul_quantize: rows of [gate(k) | up(k)]; one 256-thread CTA per row.
+cudaError_t launch_swiglu_quantize(const void* x, int8_t* q, float* s, int m, int k, cudaStream_t stream) {
+  // the SwiGLU is arithmetic-heavy (expf, a division), so rows are spread over 512 threads to keep
+  // twice as many warps resident as the plain quantizer would
+  const int packs = k / 8;
+#define CI8_SWIGLU(T, P) launch_quantize_vec<T, P, true>(x, q, s, m, k, m, 0, stream)
+  if (packs <= 256) CI8_SWIGLU(256, 1);
+  else if (packs <= 512) CI8_SWIGLU(512, 1);
+  else if (packs <= 1024) CI8_SWIGLU(512, 2);
+  else if (packs <= 1536) CI8_SWIGLU(512, 3);
+  else if (packs <= 2560) CI8_SWIGLU(512, 5);
+  else if (packs <= 4608) CI8_SWIGLU(512, 9);
+  else CI8_SWIGLU(512, 16);
+#undef CI8_SWIGLU
   return cudaGetLastError();
 }
 
@@ -366,6 +384,23 @@ int ci8_quantize_grouped4096(const void* x, int8_t* codes, float* scales, int m,
   if (m == 0) return 0;
   if (!x || !codes || !scales || !aligned(x, 16) || !aligned(codes, 8) || !aligned(scales, 4)) return kInvalid;
   return launch_quantize(x, codes, scales, m * groups, 4096, m, groups, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ci8_silu_mul(const void* x, void* out, int m, int k, ci8_stream_t stream) {
+  if (m < 0 || k <= 0 || k % 8 != 0 || static_cast<long long>(m) * 2 * k > INT32_MAX) return kInvalid;
+  if (m == 0) return 0;
+  if (!x || !out || !aligned(x, 16) || !aligned(out, 16)) return kInvalid;
+  const int64_t packs = static_cast<int64_t>(m) * (k / 8);
+  silu_mul_kernel<<<static_cast<unsigned>((packs + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint16_t*>(x), static_cast<uint16_t*>(out), packs, k / 8);
+  return cudaGetLastError();
+}
+
+int ci8_silu_mul_quantize(const void* x, int8_t* codes, float* scales, int m, int k, ci8_stream_t stream) {
+  if (m < 0 || k <= 0 || k % 8 != 0 || k > 65536 || static_cast<long long>(m) * 2 * k > INT32_MAX) return kInvalid;
+  if (m == 0) return 0;
+  if (!x || !codes || !scales || !aligned(x, 16) || !aligned(codes, 8)) return kInvalid;
+  return launch_swiglu_quantize(x, codes, scales, m, k, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int ci8_fused_channel_mm(const int8_t* a, const int8_t* w, const float* a_scale, const void* w_scale,

@@ -73,31 +73,58 @@ __device__ __forceinline__ int64_t output_row_of(int64_t i, int m, int groups) {
   return groups > 0 ? (i % groups) * static_cast<int64_t>(m) + i / groups : i;
 }
 
-template <int kTeam, int kPacks>
+// SwiGLU of one gate/up pair as the reference computes it (csrc/silu_quant.cu:30-33 in the
+// reference): silu = gate / (1 + expf(-gate)) with the fast division, product rounded to BF16.
+__device__ __forceinline__ float swiglu_one(float gate, float up) {
+  const float silu = __fdividef(gate, 1.f + expf(-gate));
+  return __fmul_rn(silu, up);
+}
+__device__ __forceinline__ uint32_t swiglu_pair(uint32_t gate, uint32_t up) {
+  __nv_bfloat162 r = __floats2bfloat162_rn(swiglu_one(bf16_lo(gate), bf16_lo(up)),
+                                           swiglu_one(bf16_hi(gate), bf16_hi(up)));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint4 swiglu_pack(const uint4& gate, const uint4& up) {
+  return make_uint4(swiglu_pair(gate.x, up.x), swiglu_pair(gate.y, up.y), swiglu_pair(gate.z, up.z),
+                    swiglu_pair(gate.w, up.w));
+}
+
+// Loads one row as 16-byte packs of BF16. kSwiGLU: the input row is [gate(k) | up(k)] and the
+// packs hold bf16(silu(gate) * up), i.e. exactly what a separate silu_mul would have written.
+template <int kTeam, int kPacks, bool kSwiGLU = false>
 __device__ __forceinline__ void load_row(uint4 (&pack)[kPacks], const uint16_t* x, int64_t row, int64_t rows,
                                          int k, int member) {
-  const uint4* src = reinterpret_cast<const uint4*>(x + (row < rows ? row : 0) * k);
+  const int64_t pitch = kSwiGLU ? 2 * static_cast<int64_t>(k) : k;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (row < rows ? row : 0) * pitch);
   const int packs_in_row = k >> 3;
 #pragma unroll
   for (int i = 0; i < kPacks; ++i) {
     const int index = i * kTeam + member;
-    pack[i] = (row < rows && index < packs_in_row) ? __ldg(src + index) : make_uint4(0, 0, 0, 0);
+    const bool live = row < rows && index < packs_in_row;
+    if constexpr (kSwiGLU) {
+      pack[i] = live ? swiglu_pack(__ldg(src + index), __ldg(src + packs_in_row + index)) : make_uint4(0, 0, 0, 0);
+    } else {
+      pack[i] = live ? __ldg(src + index) : make_uint4(0, 0, 0, 0);
+    }
   }
 }
 
-// kTeam threads per row (32 or 256), kPacks 16-byte packs per thread; 256 threads per CTA.
-// Rows of up to 3 packs per thread run one team per row with many small CTAs resident (measured
+// kTeam threads per row (32, 256 or 512), kPacks 16-byte packs per thread; 256 threads per CTA
+// (512 when the team is that wide). Rows of up to 3 packs per thread run one team per row with many small CTAs resident (measured
 // faster there); wider rows (4..9 packs) use a persistent grid in which a team strides over the
 // rows and loads its next row before it reduces and converts the current one, so loads stay in
 // flight during the arithmetic. The code is the same: the launch decides the grid.
 // Requires 16-byte aligned rows of x (k % 8 == 0, base aligned) and 8-byte aligned q.
-template <int kTeam, int kPacks>
-__global__ void __launch_bounds__(256)
+// kSwiGLU fuses silu(gate)*up in front of the quantizer (silu_mul_quantize).
+template <int kTeam, int kPacks, bool kSwiGLU = false>
+__global__ void __launch_bounds__(kTeam > 256 ? kTeam : 256)
 quantize_rows_vec_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
                          float* __restrict__ scales, int rows, int k, int m, int groups) {
-  constexpr int kRowsPerCta = 256 / kTeam;
-  constexpr bool kPrefetch = kPacks >= 4 && kPacks <= 9;
-  __shared__ float maxima[2][8];
+  constexpr int kThreads = kTeam > 256 ? kTeam : 256;   // a team wider than 256 threads is one CTA
+  constexpr int kRowsPerCta = kThreads / kTeam;
+  constexpr int kWarps = kThreads / 32;
+  constexpr bool kPrefetch = !kSwiGLU && kPacks >= 4 && kPacks <= 9;
+  __shared__ float maxima[2][kWarps];
   const int member = threadIdx.x % kTeam;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kRowsPerCta;
   const int packs_in_row = k >> 3;
@@ -105,10 +132,10 @@ quantize_rows_vec_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
 
   uint4 pack[kPacks];
   uint4 next[kPrefetch ? kPacks : 1];
-  load_row<kTeam, kPacks>(pack, x, row, rows, k, member);
+  load_row<kTeam, kPacks, kSwiGLU>(pack, x, row, rows, k, member);
   for (int64_t base = static_cast<int64_t>(blockIdx.x) * kRowsPerCta, iter = 0; base < rows;
        base += stride, row += stride, ++iter) {
-    if constexpr (kPrefetch) load_row<kTeam, kPacks>(next, x, row + stride, rows, k, member);
+    if constexpr (kPrefetch) load_row<kTeam, kPacks, kSwiGLU>(next, x, row + stride, rows, k, member);
     float maximum = 0.f;
 #pragma unroll
     for (int i = 0; i < kPacks; ++i) {
@@ -122,13 +149,13 @@ quantize_rows_vec_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
 #pragma unroll
     for (int mask = 16; mask; mask >>= 1)
       maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, mask));
-    if constexpr (kTeam == 256) {
+    if constexpr (kTeam >= 256) {
       float* slot = maxima[iter & 1];      // alternating slots: one barrier per row is enough
       if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = maximum;
       __syncthreads();
       maximum = slot[0];
 #pragma unroll
-      for (int i = 1; i < 8; ++i) maximum = fmaxf(maximum, slot[i]);
+      for (int i = 1; i < kWarps; ++i) maximum = fmaxf(maximum, slot[i]);
     }
     const float scale = fmaxf(__fdiv_rn(maximum, 127.f), 1e-20f);
     const float inverse = __fdiv_rn(1.f, scale);
@@ -146,9 +173,20 @@ quantize_rows_vec_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
 #pragma unroll
       for (int i = 0; i < kPacks; ++i) pack[i] = next[i];
     } else {
-      load_row<kTeam, kPacks>(pack, x, row + stride, rows, k, member);
+      load_row<kTeam, kPacks, kSwiGLU>(pack, x, row + stride, rows, k, member);
     }
   }
+}
+
+// silu_mul: out[m, k] = bf16(silu(x[m, :k]) * x[m, k:]); one 16-byte pack of outputs per thread.
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, int64_t packs, int packs_in_row) {
+  const int64_t index = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (index >= packs) return;
+  const int64_t row = index / packs_in_row;
+  const int col = static_cast<int>(index - row * packs_in_row);
+  const uint4* src = reinterpret_cast<const uint4*>(x) + row * 2 * packs_in_row;
+  reinterpret_cast<uint4*>(out)[index] = swiglu_pack(__ldg(src + col), __ldg(src + packs_in_row + col));
 }
 
 // Any width and alignment: one CTA per row, two passes over the row (the second one hits L1/L2).

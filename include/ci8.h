@@ -35,6 +35,17 @@ int ci8_quantize_rows(const void* x, int8_t* codes, float* scales, int m, int k,
 int ci8_quantize_grouped4096(const void* x, int8_t* codes, float* scales, int m, int groups,
                              ci8_stream_t stream);
 
+/* Replaces silu_mul (reference csrc/silu_quant.h, csrc/silu_quant.cu:64-88): x BF16 [m, 2k] holds
+ * gate | up per row; out BF16 [m,k] = bf16(silu(gate) * up), silu = gate / (1 + expf(-gate)).
+ * The reference accepts k = 8704 or 17408; any k % 8 == 0 is accepted here. 16-byte aligned. */
+int ci8_silu_mul(const void* x, void* out, int m, int k, ci8_stream_t stream);
+
+/* Replaces silu_mul_quantize (reference csrc/silu_quant.cu:10-62,77-83): the same SwiGLU fused in
+ * front of the row quantizer; bit-identical to ci8_silu_mul followed by ci8_quantize_rows.
+ * codes INT8 [m,k], scales FP32 [m]; k % 8 == 0, k <= 65536; x 16-byte, codes 8-byte aligned. */
+int ci8_silu_mul_quantize(const void* x, int8_t* codes, float* scales, int m, int k,
+                          ci8_stream_t stream);
+
 /* Replaces fused_channel_mm (reference csrc/kernels.h:27-29, csrc/fused_mm.cu:66-93).
  * a INT8 [m,k], w INT8 [n,k], a_scale FP32 [m], w_scale BF16 [n] -> out BF16 [m,n],
  * out = bf16((float(sum_k a*w) * a_scale[row]) * float(w_scale[col])).

@@ -37,6 +37,7 @@ __all__ = [
     "channel_gemv_fp64",
     "grouped_channel_mm_ref",
     "quantize_channel_ref",
+    "silu_mul_ref",
 ]
 
 
@@ -168,6 +169,23 @@ def grouped_channel_mm_ref(codes, scales, w, w_scale, fast: bool = False) -> tor
         term = acc.float() * scales[g].float()[:, None]
         total = term if g == 0 else total + term
     return (total * w_scale.float()[None, :]).bfloat16()
+
+
+# --------------------------------------------------------------------------- #
+# SwiGLU in front of the down projection (floating point: tolerance, not bit-exact)
+# --------------------------------------------------------------------------- #
+def silu_mul_ref(x: torch.Tensor) -> torch.Tensor:
+    """BF16 [M, 2K] = gate | up  ->  BF16 [M, K] = bf16(silu(gate) * up), evaluated in FP64.
+
+    The reference computes ``gate / (1 + expf(-gate))`` with the GPU's fast division and rounds
+    the FP32 product to BF16 (csrc/silu_quant.cu:30-33); its own test compares with a compiled
+    torch SwiGLU on the GPU (tests/test_cuda_ops.py:874-911). Transcendentals cannot be restated
+    bit-exactly on a CPU, so this checker is used with a tolerance of one BF16 ulp; the integer
+    part of that operator (the quantizer behind it) is checked exactly.
+    """
+    k = x.shape[1] // 2
+    gate, up = x[:, :k].double(), x[:, k:].double()
+    return (gate / (1.0 + torch.exp(-gate)) * up).to(torch.bfloat16)
 
 
 # --------------------------------------------------------------------------- #
