@@ -352,6 +352,20 @@ cudaError_t launch_gemv(const void* x, const int8_t* w, const void* sw, void* ou
   return cudaGetLastError();
 }
 
+// Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever arrives on. The
+// wait gives up after `deadline_ns`, raises the status bit and the kernel returns normally.
+__global__ void wait_timeout_selftest_kernel(unsigned long long deadline_ns, int* gave_up) {
+  __shared__ alignas(8) unsigned long long barrier;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&barrier), 1);
+    fence_barrier_init();
+    const bool completed = mbar_wait(smem_u32(&barrier), 0u, &abort_flag, deadline_ns);
+    *gave_up = completed ? 0 : 1;
+  }
+}
+
 }  // namespace
 
 // ====================================================================== C ABI
@@ -512,6 +526,13 @@ int ci8_fused_channel_mm_gather(const int8_t* a, const int8_t* w, const float* a
   const bool pair = schedule == 0 ? m > 128 : (schedule % 2 == 0);
   return pair ? launch_gemm<2, kModeFused>(a, w, p, s, outputs, world)
               : launch_gemm<1, kModeFused>(a, w, p, s, outputs, world);
+}
+
+int ci8_selftest_wait_timeout(unsigned deadline_us, int* gave_up, ci8_stream_t stream) {
+  if (!gave_up || deadline_us == 0 || deadline_us > 1000000) return kInvalid;   // at most one second
+  wait_timeout_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<unsigned long long>(deadline_us) * 1000ull, gave_up);
+  return cudaGetLastError();
 }
 
 // Test hook: the decode kernel with a forced split-K factor (1, 2 or 4); weights_biased != 0

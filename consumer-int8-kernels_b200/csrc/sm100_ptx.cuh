@@ -92,14 +92,15 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 // Bounded wait. Returns false when the wait was abandoned: either this waiter ran past the
 // deadline (it then raises *abort and the global status bit) or another role already aborted.
 template <bool kCluster = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort,
+                                          unsigned long long deadline_ns = kWaitDeadlineNs) {
   if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
   const unsigned long long start = global_timer_ns();
   for (uint32_t spin = 1;; ++spin) {
     if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 0u) {
       if (*abort) return false;
-      if (global_timer_ns() - start > kWaitDeadlineNs) {
+      if (global_timer_ns() - start > deadline_ns) {
         *abort = 1;
         atomicOr(&g_ci8_status, kStatusWaitTimeout);
         return false;

@@ -106,6 +106,12 @@ int ci8_decode_mm_split(const int8_t* a, const void* w, const float* a_scale, co
                         int32_t* workspace, void* out, int m, int n, int k, int split,
                         int weights_biased, ci8_stream_t stream);
 
+/* Self-test of the kernels' bounded waits (no counterpart in the reference): launches one CTA that
+ * waits on a barrier nothing arrives on; after deadline_us microseconds (1..1000000) the wait
+ * gives up exactly as the production kernels' waits do after their 2 s deadline: status bit 0 is
+ * raised, *gave_up (a device int) is set to 1 and the kernel returns, leaving the context usable. */
+int ci8_selftest_wait_timeout(unsigned deadline_us, int* gave_up, ci8_stream_t stream);
+
 /* Reads and clears the current device's kernel status word (synchronises the device). Bit 0: a
  * bounded wait inside a kernel ran past its deadline and the kernel gave up (its output is then
  * undefined). Returns 0 or a cudaError_t. Not for use during stream capture. */

@@ -243,3 +243,23 @@ def test_quantize_then_mm_pipeline_matches_checker(ops):
     assert_bit_equal(out, want, "out")
     ops.fused_channel_mm(codes, inputs.w.to(DEV), scales, inputs.w_scale.to(DEV), out)
     assert_bit_equal(out, want, "signed-weight out")
+
+
+def test_a_wait_that_runs_out_sets_the_status_word_and_leaves_the_context_usable(ops):
+    """Failure detection without faulting the GPU: a kernel waits on a barrier that nothing ever
+    arrives on; its bounded wait gives up after 20 ms, the status word reads 1, and the very next
+    launches on the same context are correct."""
+    assert device_status(ops) == 0
+    gave_up = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert ops.libci8.ci8_selftest_wait_timeout(20000, ctypes.c_void_p(gave_up.data_ptr()), stream) == 0
+    torch.cuda.synchronize()
+    assert gave_up.item() == 1
+    assert device_status(ops) == 1          # bit 0: a wait ran past its deadline
+    assert device_status(ops) == 0          # reading clears it
+    a, w, sa, sw = linear_case(200, 256, 512, seed=1)
+    out = torch.empty(200, 256, dtype=torch.bfloat16, device=DEV)
+    ops.fused_channel_mm(a.to(DEV), w.to(DEV), sa.to(DEV), sw.to(DEV), out)
+    _, want = ref.fused_channel_mm_ref(a, w, sa, sw)
+    assert_bit_equal(out, want, "GEMM after a timed-out wait")
+    assert device_status(ops) == 0
