@@ -9,6 +9,7 @@
 #include <atomic>
 #include <cstdint>
 
+#include "allspark_unpack.cuh"
 #include "decode_splitk.cuh"
 #include "gemm_tcgen05.cuh"
 #include "gemv_w8a16.cuh"
@@ -398,6 +399,18 @@ int ci8_quantize_grouped4096(const void* x, int8_t* codes, float* scales, int m,
   if (m == 0) return 0;
   if (!x || !codes || !scales || !aligned(x, 16) || !aligned(codes, 8) || !aligned(scales, 4)) return kInvalid;
   return launch_quantize(x, codes, scales, m * groups, 4096, m, groups, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ci8_unpack_allspark(const uint8_t* packed, const void* packed_scales, int8_t* weight, void* scales, int n,
+                        int k, ci8_stream_t stream) {
+  if (!packed || !packed_scales || !weight || !scales || n <= 0 || n % 16 != 0 || k <= 0 || k > 65536 ||
+      k % 16 != 0 || static_cast<long long>((n + 31) / 32 * 32) * k > INT32_MAX || !aligned(packed, 16) ||
+      !aligned(weight, 16))
+    return kInvalid;
+  const long long cells = static_cast<long long>((n + 31) / 32 * 8) * (k / 16);
+  unpack_allspark_kernel<<<static_cast<unsigned>((cells + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      packed, static_cast<const uint16_t*>(packed_scales), weight, static_cast<uint16_t*>(scales), n, k);
+  return cudaGetLastError();
 }
 
 int ci8_silu_mul(const void* x, void* out, int m, int k, ci8_stream_t stream) {

@@ -35,6 +35,13 @@ int ci8_quantize_rows(const void* x, int8_t* codes, float* scales, int m, int k,
 int ci8_quantize_grouped4096(const void* x, int8_t* codes, float* scales, int m, int groups,
                              ci8_stream_t stream);
 
+/* Replaces unpack_allspark (reference csrc/kernels.h, csrc/allspark_layout.cu:8-35): packed UINT8
+ * [ceil(n/32)*32, k] in AllSpark N32K16 order with permuted BF16 packed_scales [ceil(n/32)*32] ->
+ * weight INT8 [n,k] (code - 128, row-major) and scales BF16 [n]. n % 16 == 0, k % 16 == 0,
+ * k <= 65536; packed and weight 16-byte aligned (the reference asks 4 bytes of packed). */
+int ci8_unpack_allspark(const uint8_t* packed, const void* packed_scales, int8_t* weight,
+                        void* scales, int n, int k, ci8_stream_t stream);
+
 /* Replaces silu_mul (reference csrc/silu_quant.h, csrc/silu_quant.cu:64-88): x BF16 [m, 2k] holds
  * gate | up per row; out BF16 [m,k] = bf16(silu(gate) * up), silu = gate / (1 + expf(-gate)).
  * The reference accepts k = 8704 or 17408; any k % 8 == 0 is accepted here. 16-byte aligned. */

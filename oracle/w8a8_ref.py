@@ -38,6 +38,8 @@ __all__ = [
     "grouped_channel_mm_ref",
     "quantize_channel_ref",
     "silu_mul_ref",
+    "unpack_allspark_ref",
+    "pack_allspark_ref",
 ]
 
 
@@ -197,3 +199,51 @@ def quantize_channel_ref(weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tens
     scale = value.abs().amax(dim=1).clamp_min(torch.finfo(torch.float32).tiny) / 127.0
     codes = (value / scale[:, None]).round().clamp(-128, 127)
     return (codes.to(torch.int16) + 128).to(torch.uint8), scale.to(torch.bfloat16)
+
+
+# --------------------------------------------------------------------------- #
+# AllSpark N32K16 storage (byte permutation). Parity for this operator is UNPINNED: the
+# reference's only pin packs with vLLM's allspark_repack_weight (tests/test_cuda_ops.py:440-471),
+# which is not available here; the inverse permutation below restates the reference's kernel
+# index arithmetic (csrc/allspark_layout.cu:8-28), and pack_allspark_ref is its algebraic inverse.
+# --------------------------------------------------------------------------- #
+def _cell_index(n: int, k: int):
+    """For every (row, tile, j): byte offset into the packed buffer, following the reference."""
+    import numpy as np
+
+    rows = np.arange(n)[:, None, None]
+    tiles = np.arange(k // 16)[None, :, None]
+    j = np.arange(16)[None, None, :]
+    packed_row = (rows // 32) * 8 + rows % 8
+    base = packed_row * k * 4 + tiles * 64 + ((rows % 32) // 16) * 8 + ((rows % 16) // 8) * 4
+    # restored word x = (a & 0xffff) | (b << 16): bytes a0 a1 b0 b1; y: c0 c1 d0 d1; z: a2 a3 b2 b3; w: c2 c3 d2 d3
+    quarter = np.array([0, 0, 1, 1, 2, 2, 3, 3, 0, 0, 1, 1, 2, 2, 3, 3])[j]
+    byte = np.array([0, 1, 0, 1, 0, 1, 0, 1, 2, 3, 2, 3, 2, 3, 2, 3])[j]
+    return base + quarter * 16 + byte
+
+
+def unpack_allspark_ref(packed: torch.Tensor, packed_scales: torch.Tensor, n: int, k: int):
+    """packed UINT8 [ceil(n/32)*32, k] -> (INT8 [n,k] = code - 128, BF16 [n] scales)."""
+    import numpy as np
+
+    flat = packed.contiguous().view(-1).numpy()
+    index = _cell_index(n, k)
+    codes = (flat[index].reshape(n, k).astype(np.int16) - 128).astype(np.int8)
+    rows = np.arange(n)
+    scale_index = (rows // 32) * 32 + (rows % 8) * 4 + (rows % 32) // 8
+    return torch.from_numpy(codes), packed_scales[torch.from_numpy(scale_index)]
+
+
+def pack_allspark_ref(codes_u8: torch.Tensor, scales: torch.Tensor):
+    """UINT8 code+128 [n,k] and BF16 [n] scales -> the packed pair (inverse of unpack_allspark_ref)."""
+    import numpy as np
+
+    n, k = codes_u8.shape
+    padded = (n + 31) // 32 * 32
+    flat = np.zeros(padded * k, dtype=np.uint8)
+    flat[_cell_index(n, k).reshape(-1)] = codes_u8.contiguous().numpy().reshape(-1)
+    rows = np.arange(n)
+    scale_index = (rows // 32) * 32 + (rows % 8) * 4 + (rows % 32) // 8
+    packed_scales = torch.zeros(padded, dtype=scales.dtype)
+    packed_scales[torch.from_numpy(scale_index)] = scales
+    return torch.from_numpy(flat).view(padded, k), packed_scales

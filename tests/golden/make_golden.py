@@ -54,10 +54,13 @@ def weight_encoding(root: Path) -> dict:
         weight[0] = 0
         codes, scale = q.quantize_channel(weight)
         restored = q.dequantize_channel(codes, scale)
+        g_codes, g_scale = q.quantize_group32(weight)
         cases.append(dict(name=f"seed{100 + seed}", seed=100 + seed, n=n, k=k, codes_sha256=sha(codes),
                           scale_sha256=sha(scale), dequantized_sha256=sha(restored),
                           first_row_codes=codes[1, :16].tolist(),
-                          first_scales_bits=scale.view(torch.int16)[:8].tolist()))
+                          first_scales_bits=scale.view(torch.int16)[:8].tolist(),
+                          group32_codes_sha256=sha(g_codes), group32_scale_sha256=sha(g_scale),
+                          group32_dequantized_sha256=sha(q.dequantize_group32(g_codes, g_scale))))
     return dict(source="reference src/consumer_int8/quantization.py (imported)", cases=cases)
 
 

@@ -1,0 +1,68 @@
+"""unpack_allspark: the GPU kernel against the CPU restatement of the reference's index arithmetic,
+on cells packed by the algebraic inverse; shapes of the reference's test
+(tests/test_cuda_ops.py:440-471), graph replay on repacked inputs."""
+import pytest
+import torch
+
+from gpu_common import DEV, assert_bit_equal, guarded
+from oracle import w8a8_ref as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n,k", [(16, 16), (48, 80), (128, 512), (5120, 3072), (34816, 5120)])
+def test_allspark_unpack_preserves_every_code_and_scale_in_graph(ops, n, k):
+    generator = torch.Generator().manual_seed(319)
+    codes = torch.randint(0, 256, (n, k), dtype=torch.uint8, generator=generator)
+    scales = torch.randn(n, generator=generator).bfloat16()
+    packed_cpu, packed_scales_cpu = ref.pack_allspark_ref(codes, scales)
+    packed, packed_scales = packed_cpu.to(DEV), packed_scales_cpu.to(DEV)
+    restored, check_w = guarded((n, k), torch.int8, 77)
+    restored_scales, check_s = guarded((n,), torch.bfloat16, float("nan"))
+    graph = torch.cuda.CUDAGraph()
+    ops.unpack_allspark(packed, packed_scales, restored, restored_scales)
+    with torch.cuda.graph(graph):
+        ops.unpack_allspark(packed, packed_scales, restored, restored_scales)
+    for _ in range(2):
+        restored.zero_()
+        restored_scales.zero_()
+        graph.replay()
+        want_codes, want_scales = ref.unpack_allspark_ref(packed.cpu(), packed_scales.cpu(), n, k)
+        assert_bit_equal(restored, want_codes, "codes vs checker")
+        assert_bit_equal(restored_scales, want_scales, "scales vs checker")
+        assert torch.equal(restored.cpu(), (codes.short() - 128).to(torch.int8))     # lossless round trip
+        assert torch.equal(restored_scales.cpu().view(torch.int16), scales.view(torch.int16))
+        check_w()
+        check_s()
+        codes.bitwise_xor_(255)
+        scales.neg_()
+        changed, changed_scales = ref.pack_allspark_ref(codes, scales)
+        packed.copy_(changed)
+        packed_scales.copy_(changed_scales)
+
+
+def test_unpacked_weights_feed_the_gemm(ops):
+    """unpack_allspark -> quantize_rows -> fused_channel_mm, the chain of
+    benchmarks/microbench.py:46-53 in the reference, equals channel_mm on the UINT8 codes."""
+    from consumer_int8 import workloads
+
+    inputs = workloads.linear_inputs(64, 256, 512, seed=9)
+    packed, packed_scales = ref.pack_allspark_ref(inputs.w_u8, inputs.w_scale)
+    weight = torch.empty(256, 512, dtype=torch.int8, device=DEV)
+    scales = torch.empty(256, dtype=torch.bfloat16, device=DEV)
+    ops.unpack_allspark(packed.to(DEV), packed_scales.to(DEV), weight, scales)
+    codes = torch.empty(64, 512, dtype=torch.int8, device=DEV)
+    row_scales = torch.empty(64, device=DEV)
+    ops.quantize_rows(inputs.x.to(DEV), codes, row_scales)
+    out, direct = (torch.empty(64, 256, dtype=torch.bfloat16, device=DEV) for _ in range(2))
+    ops.fused_channel_mm(codes, weight, row_scales, scales, out)
+    ops.channel_mm(codes, inputs.w_u8.to(DEV), row_scales, inputs.w_scale.to(DEV), direct)
+    assert torch.equal(out, direct)
+
+
+def test_unpack_rejects_wrong_geometry(ops):
+    packed = torch.zeros(32, 32, dtype=torch.uint8, device=DEV)
+    packed_scales = torch.zeros(32, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError, match="AllSpark N32K16"):
+        ops.unpack_allspark(packed, packed_scales, torch.empty(24, 32, dtype=torch.int8, device=DEV),
+                            torch.empty(24, dtype=torch.bfloat16, device=DEV))

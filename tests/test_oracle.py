@@ -157,3 +157,32 @@ def test_config0_plumbing_runs_on_the_host():
     assert torch.isfinite(out.float()).all()
     _, signed = ref.fused_channel_mm_ref(codes, inputs.w, scales, inputs.w_scale, fast=True)
     assert torch.equal(out, signed)
+
+
+def test_allspark_unpack_restatement_follows_the_reference_index_arithmetic():
+    """The vectorised restatement against a literal scalar walk of the reference's kernel
+    (csrc/allspark_layout.cu:10-27) on a small case, and pack/unpack as mutual inverses."""
+    import numpy as np
+
+    n, k = 48, 32
+    g = torch.Generator().manual_seed(5)
+    packed = torch.randint(0, 256, (64, k), dtype=torch.uint8, generator=g)
+    packed_scales = torch.randn(64, generator=g).bfloat16()
+    words = packed.contiguous().view(-1).numpy().view("<u4")
+    want = np.zeros((n, k), dtype=np.int8)
+    for row in range(n):
+        for tile in range(k // 16):
+            packed_row = (row // 32) * 8 + row % 8
+            offset = packed_row * k * 4 + tile * 64 + ((row % 32) // 16) * 8 + ((row % 16) // 8) * 4
+            a, b, c, d = (int(words[offset // 4 + i]) for i in (0, 4, 8, 12))
+            restored = [((a & 0xFFFF) | (b << 16)) & 0xFFFFFFFF, ((c & 0xFFFF) | (d << 16)) & 0xFFFFFFFF,
+                        (a >> 16) | (b & 0xFFFF0000), (c >> 16) | (d & 0xFFFF0000)]
+            raw = np.array([w ^ 0x80808080 for w in restored], dtype="<u4").view(np.int8)
+            want[row, tile * 16:(tile + 1) * 16] = raw
+    codes, scales = ref.unpack_allspark_ref(packed, packed_scales, n, k)
+    assert np.array_equal(codes.numpy(), want)
+    for row in (0, 7, 8, 31, 32, 47):
+        assert scales[row] == packed_scales[(row // 32) * 32 + (row % 8) * 4 + (row % 32) // 8]
+    repacked, repacked_scales = ref.pack_allspark_ref((codes.short() + 128).to(torch.uint8), scales)
+    again, again_scales = ref.unpack_allspark_ref(repacked, repacked_scales, n, k)
+    assert torch.equal(again, codes) and torch.equal(again_scales.view(torch.int16), scales.view(torch.int16))
