@@ -488,8 +488,31 @@ int ci8_channel_gemv(const void* x, const int8_t* w, const void* w_scale, void* 
       static_cast<long long>(n) * k > INT32_MAX || !aligned(w, 16) || !aligned(x, 4))
     return kInvalid;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (aligned(x, 16) && n >= 2048) {
+    // production path: TMA-staged weights, one CTA per slab of channels, one wave
+    const int sms = sm_count();
+    int slab = ((n + sms - 1) / sms + 31) / 32 * 32;
+    if (slab < 32) slab = 32;
+    if (slab > GemvTmaConfig::kMaxSlab) slab = GemvTmaConfig::kMaxSlab;
+    static std::atomic<uint64_t> smem_done1{0}, smem_done2{0};
+    cudaError_t err = m <= 8 ? ensure_smem(gemv_w8a16_tma_kernel<1>, GemvTmaConfig::kSmemBytes, smem_done1)
+                             : ensure_smem(gemv_w8a16_tma_kernel<2>, GemvTmaConfig::kSmemBytes, smem_done2);
+    if (err != cudaSuccess) return err;
+    CUtensorMap map_w;
+    err = make_map(&map_w, w, n, k, slab);
+    if (err != cudaSuccess) return err;
+    const int ctas = (n + slab - 1) / slab;
+    const auto* xb = static_cast<const __nv_bfloat16*>(x);
+    const auto* sb = static_cast<const __nv_bfloat16*>(w_scale);
+    auto* ob = static_cast<__nv_bfloat16*>(out);
+    if (m <= 8)
+      gemv_w8a16_tma_kernel<1><<<ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s>>>(map_w, xb, sb, ob, m, n, k, slab);
+    else
+      gemv_w8a16_tma_kernel<2><<<ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s>>>(map_w, xb, sb, ob, m, n, k, slab);
+    return cudaGetLastError();
+  }
   if (aligned(x, 16)) {
-    // tensor-core path: 64 channels per CTA, K split over four warps
+    // register-fed tensor-core path: 64 channels per CTA, K split over four warps
     const int ctas = (n + kGemvChannelsPerCta - 1) / kGemvChannelsPerCta;
     const auto* xb = static_cast<const __nv_bfloat16*>(x);
     const auto* sb = static_cast<const __nv_bfloat16*>(w_scale);

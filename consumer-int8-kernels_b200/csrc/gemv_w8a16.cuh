@@ -11,10 +11,14 @@
 // four MMAs directly (the activations are read with the same permutation, so the dot products
 // are unchanged). The four K quarters of a CTA are added through shared memory.
 //
+// gemv_w8a16_tma_kernel: the same arithmetic with the weights staged through shared memory by TMA
+// (the production path); gemv_w8a16_mma_kernel keeps the register-fed loads (small N).
 // gemv_w8a16_kernel: plain FMA version for activations that are not 16-byte aligned.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cstdint>
+#include "sm100_ptx.cuh"
 
 namespace ci8 {
 
@@ -174,6 +178,178 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const int8_t* __restr
           if (channel < n && row < m) out[static_cast<size_t>(row) * n + channel] = __float2bfloat16_rn(total);
         }
       }
+  }
+}
+
+// ------------------------------------------------------------------ TMA-fed tensor-core version
+// gemv_w8a16_tma_kernel: the weight stream goes through shared memory. One producer warp issues
+// TMA tile loads of a slab of up to 256 channels x 128 K bytes into a 6-stage ring (the same
+// 128-byte-swizzled tiles the W8A8 kernels use); eight consumer warps own 32 channels each, read
+// their A fragments with ldmatrix (conflict-free on the swizzled tile; a thread receives the four
+// codes at K offsets 4t..4t+3 of a 16-wide segment, which feed one MMA through the same K
+// permutation as above), dequantise in registers and run mma.sync. Activations come from
+// global memory (L1/L2 resident), loaded one K block ahead. HBM only sees the weights, once,
+// through deep asynchronous copies instead of register-fed loads.
+struct GemvTmaConfig {
+  static constexpr int kBlockK = 128;
+  static constexpr int kMaxSlab = 256;
+  static constexpr int kStageBytes = kMaxSlab * kBlockK;   // 32 KB
+  static constexpr int kStages = 6;
+  static constexpr int kConsumerWarps = 16;   // 16 channels (one A fragment) each
+  static constexpr int kGroups = 1;            // 16-channel groups per consumer warp
+  static constexpr int kThreads = (1 + kConsumerWarps) * 32;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 256 + 1024;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+template <int kRowBlocks>
+__global__ void __launch_bounds__(GemvTmaConfig::kThreads, 1)
+gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16* __restrict__ x,
+                      const __nv_bfloat16* __restrict__ sw, __nv_bfloat16* __restrict__ out,
+                      int m, int n, int k, int slab) {
+  using Cfg = GemvTmaConfig;
+  extern __shared__ uint8_t gemv_tma_smem[];
+  const uint32_t raw_addr = smem_u32(gemv_tma_smem);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  const uint32_t smem_base = raw_addr + pad;
+  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
+  volatile int* abort_flag =
+      reinterpret_cast<volatile int*>(gemv_tma_smem + pad + Cfg::kStages * Cfg::kStageBytes + 8 * 2 * Cfg::kStages);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * slab;
+  const int num_kb = (k + Cfg::kBlockK - 1) / Cfg::kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), Cfg::kConsumerWarps);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_w);
+  }
+  __syncthreads();
+
+  if (warp == Cfg::kConsumerWarps) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx = static_cast<uint32_t>(slab) * Cfg::kBlockK;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+          __nanosleep(200000);
+          break;
+        }
+        mbar_arrive_expect_tx(full_bar(stage), tx);
+        tma_load_2d(smem_base + stage * Cfg::kStageBytes, &map_w, kb * Cfg::kBlockK, n0, full_bar(stage));
+        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ consumers
+  const int g = lane >> 2, t = lane & 3;
+  const int c_base = warp * 16 * Cfg::kGroups;        // this warp's first channel within the slab
+  const bool warp_active = c_base < slab;
+  float scale[Cfg::kGroups][2];
+#pragma unroll
+  for (int j = 0; j < Cfg::kGroups; ++j)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int channel = n0 + c_base + j * 16 + h * 8 + g;
+      scale[j][h] = (warp_active && channel < n) ? __bfloat162float(sw[channel]) : 0.f;
+    }
+  const __nv_bfloat16* x_row[kRowBlocks];
+  bool x_valid[kRowBlocks];
+#pragma unroll
+  for (int rb = 0; rb < kRowBlocks; ++rb) {
+    x_valid[rb] = rb * 8 + g < m;
+    x_row[rb] = x + static_cast<size_t>(x_valid[rb] ? rb * 8 + g : 0) * k;
+  }
+  // activations of one K block for this lane: segment s (16 K positions) -> 4 values at 4t..4t+3
+  auto load_x = [&](int kb, uint2 (&dst)[kRowBlocks][8]) {
+#pragma unroll
+    for (int rb = 0; rb < kRowBlocks; ++rb)
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const int kk = kb * Cfg::kBlockK + s * 16 + t * 4;
+        dst[rb][s] = (warp_active && kb < num_kb && x_valid[rb] && kk < k)
+                         ? __ldg(reinterpret_cast<const uint2*>(x_row[rb] + kk))
+                         : make_uint2(0u, 0u);
+      }
+  };
+  // ldmatrix lane addressing: matrix = lane / 8 -> (row half = matrix & 1, segment offset = matrix >> 1)
+  const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8;
+  const int lm_seg = lane >> 4;
+
+  float acc[Cfg::kGroups][kRowBlocks][4];
+#pragma unroll
+  for (int j = 0; j < Cfg::kGroups; ++j)
+#pragma unroll
+    for (int rb = 0; rb < kRowBlocks; ++rb)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[j][rb][i] = 0.f;
+
+  uint2 xv[kRowBlocks][8], x_next[kRowBlocks][8];
+  load_x(0, xv);
+  int stage = 0;
+  uint32_t phase = 0;
+  for (int kb = 0; kb < num_kb; ++kb) {
+    load_x(kb + 1, x_next);
+    if (!mbar_wait(full_bar(stage), phase, abort_flag)) break;
+    if (warp_active) {
+      const uint32_t tile = smem_base + stage * Cfg::kStageBytes;
+#pragma unroll
+      for (int j = 0; j < Cfg::kGroups; ++j) {
+        const int row = c_base + j * 16 + lm_row;     // slab row whose 16-byte chunk this lane addresses
+#pragma unroll
+        for (int sp = 0; sp < 4; ++sp) {              // segment pair: segments 2sp and 2sp+1
+          uint32_t frag[4];                           // (rows 0-7, seg), (rows 8-15, seg), (0-7, seg+1), (8-15, seg+1)
+          const int seg = 2 * sp + lm_seg;
+          ldmatrix_x4(frag, tile + row * 128 + ((seg ^ (row & 7)) << 4));
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t a[4];
+            dequant4(frag[2 * half] ^ 0x80808080u, scale[j][0], a[0], a[2]);
+            dequant4(frag[2 * half + 1] ^ 0x80808080u, scale[j][1], a[1], a[3]);
+#pragma unroll
+            for (int rb = 0; rb < kRowBlocks; ++rb)
+              mma_bf16_16816(acc[j][rb], a, xv[rb][2 * sp + half].x, xv[rb][2 * sp + half].y);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty_bar(stage));
+    if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+#pragma unroll
+    for (int rb = 0; rb < kRowBlocks; ++rb)
+#pragma unroll
+      for (int s = 0; s < 8; ++s) xv[rb][s] = x_next[rb][s];
+  }
+
+  if (warp_active) {
+#pragma unroll
+    for (int j = 0; j < Cfg::kGroups; ++j)
+#pragma unroll
+      for (int rb = 0; rb < kRowBlocks; ++rb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int channel = n0 + c_base + j * 16 + (i >> 1) * 8 + g;
+          const int row = rb * 8 + 2 * t + (i & 1);
+          if (channel < n && c_base + j * 16 + (i >> 1) * 8 + g < slab && row < m)
+            out[static_cast<size_t>(row) * n + channel] = __float2bfloat16_rn(acc[j][rb][i]);
+        }
   }
 }
 

@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 8, 13, 16])
-@pytest.mark.parametrize("n,k", [(37, 528), (512, 5120), (1000, 17408)])
+@pytest.mark.parametrize("n,k", [(37, 528), (512, 5120), (1000, 17408), (4096, 5120), (2500, 528), (34816, 1040)])
 def test_w8a16_small_batch_matches_bf16_dequantized_linear(ops, m, n, k):
     torch.manual_seed(134)
     x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
