@@ -90,13 +90,20 @@ cudaError_t make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
 bool aligned(const void* p, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(p) % bytes == 0; }
 
 // ------------------------------------------------------------------ tcgen05 GEMM launch
-// BF16 [rows, cols] output matrix -> store boxes of 64 columns x 32 rows with the 128-byte swizzle.
+// BF16 [rows, cols] matrix -> boxes of box_cols x box_rows elements with the 128-byte swizzle.
+cudaError_t make_bf16_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                          uint32_t box_rows);
+// BF16 [rows, cols] output matrix -> store boxes of 64 columns x 32 rows.
 cudaError_t make_output_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols) {
+  return make_bf16_map(map, base, rows, cols, 64, 32);
+}
+cudaError_t make_bf16_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                          uint32_t box_rows) {
   EncodeTiled encode = encode_tiled_fn();
   if (!encode) return cudaErrorNotSupported;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {64u, 32u};
+  const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t elem[2] = {1u, 1u};
   const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box,
                             elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -498,17 +505,18 @@ int ci8_channel_gemv(const void* x, const int8_t* w, const void* w_scale, void* 
     cudaError_t err = m <= 8 ? ensure_smem(gemv_w8a16_tma_kernel<1>, GemvTmaConfig::kSmemBytes, smem_done1)
                              : ensure_smem(gemv_w8a16_tma_kernel<2>, GemvTmaConfig::kSmemBytes, smem_done2);
     if (err != cudaSuccess) return err;
-    CUtensorMap map_w;
+    CUtensorMap map_w, map_x;
     err = make_map(&map_w, w, n, k, slab);
     if (err != cudaSuccess) return err;
+    err = make_bf16_map(&map_x, x, m, k, 64, 16);
+    if (err != cudaSuccess) return err;
     const int ctas = (n + slab - 1) / slab;
-    const auto* xb = static_cast<const __nv_bfloat16*>(x);
     const auto* sb = static_cast<const __nv_bfloat16*>(w_scale);
     auto* ob = static_cast<__nv_bfloat16*>(out);
     if (m <= 8)
-      gemv_w8a16_tma_kernel<1><<<ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s>>>(map_w, xb, sb, ob, m, n, k, slab);
+      gemv_w8a16_tma_kernel<1><<<ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s>>>(map_w, map_x, sb, ob, m, n, k, slab);
     else
-      gemv_w8a16_tma_kernel<2><<<ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s>>>(map_w, xb, sb, ob, m, n, k, slab);
+      gemv_w8a16_tma_kernel<2><<<ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s>>>(map_w, map_x, sb, ob, m, n, k, slab);
     return cudaGetLastError();
   }
   if (aligned(x, 16)) {

@@ -30,16 +30,24 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
 }
 
 // Four INT8 codes (one 32-bit word, already XORed with 0x80808080 so each byte is code+128) ->
-// two BF16 pairs bf16(code * scale): PRMT builds the float 2^23 + (code+128), one FADD removes
-// the offset exactly, one FMUL applies the scale, CVT rounds two values to a BF16 pair.
-__device__ __forceinline__ void dequant4(uint32_t biased, float scale, uint32_t& lo, uint32_t& hi) {
-  constexpr float kOffset = 8388608.f + 128.f;
-  const float c0 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7650)), kOffset);
-  const float c1 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7651)), kOffset);
-  const float c2 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7652)), kOffset);
-  const float c3 = __fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7653)), kOffset);
-  __nv_bfloat162 p0 = __floats2bfloat162_rn(__fmul_rn(c0, scale), __fmul_rn(c1, scale));
-  __nv_bfloat162 p1 = __floats2bfloat162_rn(__fmul_rn(c2, scale), __fmul_rn(c3, scale));
+// two BF16 pairs bf16(code * scale). PRMT builds the float f = 2^23 + (code+128); one FMA gives
+// f*scale - (2^23+128)*scale = code*scale, exactly: the subtrahend is exact in FP32 because a BF16
+// scale has 8 significant bits and (2^16+1)*m fits 24 bits, and |code|*m fits 16 bits, so the FMA
+// rounds nothing and equals the reference's float(code)*scale; CVT then rounds pairs to BF16.
+struct DequantScale {
+  float scale;
+  float offset;   // -(2^23 + 128) * scale
+};
+__device__ __forceinline__ DequantScale make_dequant_scale(float scale) {
+  return DequantScale{scale, -__fmul_rn(8388736.f, scale)};
+}
+__device__ __forceinline__ void dequant4(uint32_t biased, const DequantScale& s, uint32_t& lo, uint32_t& hi) {
+  const float c0 = __fmaf_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7650)), s.scale, s.offset);
+  const float c1 = __fmaf_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7651)), s.scale, s.offset);
+  const float c2 = __fmaf_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7652)), s.scale, s.offset);
+  const float c3 = __fmaf_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7653)), s.scale, s.offset);
+  __nv_bfloat162 p0 = __floats2bfloat162_rn(c0, c1);
+  __nv_bfloat162 p1 = __floats2bfloat162_rn(c2, c3);
   lo = *reinterpret_cast<uint32_t*>(&p0);
   hi = *reinterpret_cast<uint32_t*>(&p1);
 }
@@ -66,7 +74,7 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const int8_t* __restr
 
   // channels of this lane's A-fragment rows: group j, rows g and g + 8
   const int8_t* w_row[2][2];
-  float scale[2][2];
+  DequantScale scale[2][2];
   bool valid[2][2];
 #pragma unroll
   for (int j = 0; j < 2; ++j)
@@ -75,7 +83,7 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const int8_t* __restr
       const int channel = c_base + j * 16 + h * 8 + g;
       valid[j][h] = channel < n;
       w_row[j][h] = w + static_cast<size_t>(valid[j][h] ? channel : 0) * k;
-      scale[j][h] = valid[j][h] ? __bfloat162float(sw[channel]) : 0.f;
+      scale[j][h] = make_dequant_scale(valid[j][h] ? __bfloat162float(sw[channel]) : 0.f);
     }
   const __nv_bfloat16* x_row[kRowBlocks];
   bool x_valid[kRowBlocks];
@@ -187,16 +195,19 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const int8_t* __restr
 // 128-byte-swizzled tiles the W8A8 kernels use); eight consumer warps own 32 channels each, read
 // their A fragments with ldmatrix (conflict-free on the swizzled tile; a thread receives the four
 // codes at K offsets 4t..4t+3 of a 16-wide segment, which feed one MMA through the same K
-// permutation as above), dequantise in registers and run mma.sync. Activations come from
-// global memory (L1/L2 resident), loaded one K block ahead. HBM only sees the weights, once,
+// permutation as above), dequantise in registers and run mma.sync. The 16 x 128 activation tile of
+// each K block rides in the same stage (two swizzled TMA boxes) and is read with conflict-free
+// 8-byte shared loads. HBM only sees the weights, once,
 // through deep asynchronous copies instead of register-fed loads.
 struct GemvTmaConfig {
   static constexpr int kBlockK = 128;
   static constexpr int kMaxSlab = 256;
-  static constexpr int kStageBytes = kMaxSlab * kBlockK;   // 32 KB
+  static constexpr int kWeightBytes = kMaxSlab * kBlockK;   // 32 KB of weights per stage
+  static constexpr int kXBoxBytes = 16 * 128;               // 16 activation rows x 64 BF16
+  static constexpr int kStageBytes = kWeightBytes + 2 * kXBoxBytes;   // + the 128 K positions of x
   static constexpr int kStages = 6;
-  static constexpr int kConsumerWarps = 16;   // 16 channels (one A fragment) each
-  static constexpr int kGroups = 1;            // 16-channel groups per consumer warp
+  static constexpr int kConsumerWarps = 8;
+  static constexpr int kGroups = 2;            // 16-channel groups (A fragments) per consumer warp
   static constexpr int kThreads = (1 + kConsumerWarps) * 32;
   static constexpr int kSmemBytes = kStages * kStageBytes + 256 + 1024;
 };
@@ -206,10 +217,16 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
 
+// map_x: BF16 activations [m, k] as boxes of 64 columns x 16 rows (rows past m read as zero).
 template <int kRowBlocks>
 __global__ void __launch_bounds__(GemvTmaConfig::kThreads, 1)
-gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bfloat16* __restrict__ x,
+gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       const __nv_bfloat16* __restrict__ sw, __nv_bfloat16* __restrict__ out,
                       int m, int n, int k, int slab) {
   using Cfg = GemvTmaConfig;
@@ -235,6 +252,7 @@ gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bflo
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
   }
   __syncthreads();
 
@@ -243,14 +261,17 @@ gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bflo
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      const uint32_t tx = static_cast<uint32_t>(slab) * Cfg::kBlockK;
+      const uint32_t tx = static_cast<uint32_t>(slab) * Cfg::kBlockK + 2 * Cfg::kXBoxBytes;
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
           __nanosleep(200000);
           break;
         }
         mbar_arrive_expect_tx(full_bar(stage), tx);
-        tma_load_2d(smem_base + stage * Cfg::kStageBytes, &map_w, kb * Cfg::kBlockK, n0, full_bar(stage));
+        const uint32_t dst = smem_base + stage * Cfg::kStageBytes;
+        tma_load_2d(dst, &map_w, kb * Cfg::kBlockK, n0, full_bar(stage));
+        tma_load_2d(dst + Cfg::kWeightBytes, &map_x, kb * Cfg::kBlockK, 0, full_bar(stage));
+        tma_load_2d(dst + Cfg::kWeightBytes + Cfg::kXBoxBytes, &map_x, kb * Cfg::kBlockK + 64, 0, full_bar(stage));
         if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
       }
     }
@@ -261,33 +282,14 @@ gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bflo
   const int g = lane >> 2, t = lane & 3;
   const int c_base = warp * 16 * Cfg::kGroups;        // this warp's first channel within the slab
   const bool warp_active = c_base < slab;
-  float scale[Cfg::kGroups][2];
+  DequantScale scale[Cfg::kGroups][2];
 #pragma unroll
   for (int j = 0; j < Cfg::kGroups; ++j)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int channel = n0 + c_base + j * 16 + h * 8 + g;
-      scale[j][h] = (warp_active && channel < n) ? __bfloat162float(sw[channel]) : 0.f;
+      scale[j][h] = make_dequant_scale((warp_active && channel < n) ? __bfloat162float(sw[channel]) : 0.f);
     }
-  const __nv_bfloat16* x_row[kRowBlocks];
-  bool x_valid[kRowBlocks];
-#pragma unroll
-  for (int rb = 0; rb < kRowBlocks; ++rb) {
-    x_valid[rb] = rb * 8 + g < m;
-    x_row[rb] = x + static_cast<size_t>(x_valid[rb] ? rb * 8 + g : 0) * k;
-  }
-  // activations of one K block for this lane: segment s (16 K positions) -> 4 values at 4t..4t+3
-  auto load_x = [&](int kb, uint2 (&dst)[kRowBlocks][8]) {
-#pragma unroll
-    for (int rb = 0; rb < kRowBlocks; ++rb)
-#pragma unroll
-      for (int s = 0; s < 8; ++s) {
-        const int kk = kb * Cfg::kBlockK + s * 16 + t * 4;
-        dst[rb][s] = (warp_active && kb < num_kb && x_valid[rb] && kk < k)
-                         ? __ldg(reinterpret_cast<const uint2*>(x_row[rb] + kk))
-                         : make_uint2(0u, 0u);
-      }
-  };
   // ldmatrix lane addressing: matrix = lane / 8 -> (row half = matrix & 1, segment offset = matrix >> 1)
   const int lm_row = (lane & 7) + ((lane >> 3) & 1) * 8;
   const int lm_seg = lane >> 4;
@@ -300,20 +302,29 @@ gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bflo
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[j][rb][i] = 0.f;
 
-  uint2 xv[kRowBlocks][8], x_next[kRowBlocks][8];
-  load_x(0, xv);
   int stage = 0;
   uint32_t phase = 0;
   for (int kb = 0; kb < num_kb; ++kb) {
-    load_x(kb + 1, x_next);
     if (!mbar_wait(full_bar(stage), phase, abort_flag)) break;
     if (warp_active) {
       const uint32_t tile = smem_base + stage * Cfg::kStageBytes;
+      const uint32_t x_tile = tile + Cfg::kWeightBytes;
 #pragma unroll
-      for (int j = 0; j < Cfg::kGroups; ++j) {
-        const int row = c_base + j * 16 + lm_row;     // slab row whose 16-byte chunk this lane addresses
+      for (int sp = 0; sp < 4; ++sp) {                // segment pair: 16-wide K segments 2sp and 2sp+1
+        // B fragments: the four activations at K offsets 4t..4t+3 of each segment, row g (+8), from
+        // the swizzled x boxes (16-byte chunk c of row r lives at chunk c ^ (r & 7))
+        uint2 b[kRowBlocks][2];
 #pragma unroll
-        for (int sp = 0; sp < 4; ++sp) {              // segment pair: segments 2sp and 2sp+1
+        for (int half = 0; half < 2; ++half) {
+          const int seg = 2 * sp + half;
+          const int chunk = (seg & 3) * 2 + (t >> 1);
+          const uint32_t base = x_tile + (seg >> 2) * Cfg::kXBoxBytes + g * 128 + ((chunk ^ g) << 4) + (t & 1) * 8;
+#pragma unroll
+          for (int rb = 0; rb < kRowBlocks; ++rb) b[rb][half] = lds64(base + rb * 8 * 128);
+        }
+#pragma unroll
+        for (int j = 0; j < Cfg::kGroups; ++j) {
+          const int row = c_base + j * 16 + lm_row;   // slab row whose 16-byte chunk this lane addresses
           uint32_t frag[4];                           // (rows 0-7, seg), (rows 8-15, seg), (0-7, seg+1), (8-15, seg+1)
           const int seg = 2 * sp + lm_seg;
           ldmatrix_x4(frag, tile + row * 128 + ((seg ^ (row & 7)) << 4));
@@ -323,8 +334,7 @@ gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bflo
             dequant4(frag[2 * half] ^ 0x80808080u, scale[j][0], a[0], a[2]);
             dequant4(frag[2 * half + 1] ^ 0x80808080u, scale[j][1], a[1], a[3]);
 #pragma unroll
-            for (int rb = 0; rb < kRowBlocks; ++rb)
-              mma_bf16_16816(acc[j][rb], a, xv[rb][2 * sp + half].x, xv[rb][2 * sp + half].y);
+            for (int rb = 0; rb < kRowBlocks; ++rb) mma_bf16_16816(acc[j][rb], a, b[rb][half].x, b[rb][half].y);
           }
         }
       }
@@ -332,10 +342,6 @@ gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __nv_bflo
     __syncwarp();
     if (lane == 0) mbar_arrive(empty_bar(stage));
     if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
-#pragma unroll
-    for (int rb = 0; rb < kRowBlocks; ++rb)
-#pragma unroll
-      for (int s = 0; s < 8; ++s) xv[rb][s] = x_next[rb][s];
   }
 
   if (warp_active) {
