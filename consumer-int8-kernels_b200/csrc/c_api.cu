@@ -124,8 +124,19 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   if (err != cudaSuccess) return err;
 
   GemmParams p = base;
+  const int sms = sm_count();
+  const long long workers = kCtas == 2 ? sms / 2 : sms;
   p.tiles_m = (p.m + Cfg::kBlockM * kCtas - 1) / (Cfg::kBlockM * kCtas);
-  p.tiles_n = (p.n + Cfg::kChannelsPerTile - 1) / Cfg::kChannelsPerTile;
+  // Tile width: 256 accumulator columns unless a schedule asks for a narrower tile (a multiple of 32;
+  // schedules 3..6). Narrower tiles were tried as a cure for a mostly empty last wave (fewer, fuller
+  // waves on paper) and measured slower: a 224-wide MMA does not take less time than a 256-wide one.
+  // The biased form keeps 240 channels + 16 ones rows; the gathering form keeps 256.
+  int tile_n = kMode == kModeBiased ? Cfg::kChannelsPerTile : 256;
+  if (kMode != kModeBiased && num_outputs <= 1 && p.tile_n > 0) tile_n = p.tile_n;
+  p.tile_n = tile_n;
+  p.tiles_n = (p.n + tile_n - 1) / tile_n;
+  const int w_box_rows = kMode == kModeBiased ? Cfg::kBRowsLoad : tile_n / kCtas;
+  p.stage_tx = Cfg::kABytes + w_box_rows * Cfg::kBlockK;
   // rows of A per raster group: about 32 MiB of activations, so they stay in L2
   const long long group_rows = (32ll << 20) / (static_cast<long long>(p.k) * p.groups);
   p.group_m = static_cast<int>(group_rows / (Cfg::kBlockM * kCtas));
@@ -134,7 +145,7 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   CUtensorMap map_a, map_w;
   err = make_map(&map_a, a, static_cast<uint64_t>(p.m) * p.groups, p.k, Cfg::kBlockM);
   if (err != cudaSuccess) return err;
-  err = make_map(&map_w, w, p.n, static_cast<uint64_t>(p.k) * p.groups, Cfg::kBRowsLoad);
+  err = make_map(&map_w, w, p.n, static_cast<uint64_t>(p.k) * p.groups, w_box_rows);
   if (err != cudaSuccess) return err;
   OutputMaps out_maps = {};
   void* local_only[1] = {p.out};
@@ -156,21 +167,6 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   }
 
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
-  const int sms = sm_count();
-  // Optional (schedules 3 and 4): the tiles of the last, partial wave are cut into 2 or 4 column
-  // slices so that they spread over the idle CTAs. Off by default: on a power-capped B200 the
-  // partial wave runs at a higher clock and the narrower slices cost more energy per operation,
-  // so the measured gain was nil (not for the biased form: its row-sum column has a fixed place).
-  {
-    const long long workers = kCtas == 2 ? sms / 2 : sms;
-    const long long tail = tiles % workers;
-    int split = 1;
-    if (p.split > 1 && kMode != kModeBiased && tiles > workers && tail > 0 && tail * 2 <= workers)
-      split = tail * 4 <= workers ? 4 : 2;
-    p.split = split;
-    p.full_tiles = static_cast<int>(split > 1 ? tiles - tail : tiles);
-    p.total_items = static_cast<int>(p.full_tiles + (tiles - p.full_tiles) * split);
-  }
   cudaLaunchConfig_t config = {};
   cudaLaunchAttribute attr[1];
   if (kCtas == 2) {
@@ -449,12 +445,12 @@ int ci8_fused_channel_mm(const int8_t* a, const int8_t* w, const float* a_scale,
     return launch_decode<false>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, k, 1, 0, 0, 0, 0, 0, 1, 0};
-  // schedule 0: pairs of CTAs once there is more than one 128-row block; odd values force the
-  // single-CTA tile, even values the two-CTA tile; 3 and 4 also slice the last wave's tiles.
-  // All give identical bits.
+               m, n, k, 1, 0, 0, 0, 0, 0, 0};
+  // schedule 0: pairs of CTAs once there is more than one 128-row block, 256-wide tiles; odd values
+  // force the single-CTA tile, even values the two-CTA tile; 1/2 with 256-wide tiles, 3/4 with
+  // 224-wide, 5/6 with 192-wide tiles. All give identical bits.
   const bool pair = schedule == 0 ? m > 128 : (schedule % 2 == 0);
-  p.split = (schedule == 3 || schedule == 4) ? 2 : 1;   // > 1 requests last-wave slicing
+  p.tile_n = schedule == 0 ? 0 : schedule <= 2 ? 256 : schedule <= 4 ? 224 : 192;
   return pair ? launch_gemm<2, kModeFused>(a, w, p, s) : launch_gemm<1, kModeFused>(a, w, p, s);
 }
 
@@ -470,7 +466,7 @@ int ci8_cutlass_channel_mm(const int8_t* a, const int8_t* w, const float* a_scal
     return launch_decode<false>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), workspace,
-               m, n, k, 1, 0, 0, 0, 0, 0, 1, 0};
+               m, n, k, 1, 0, 0, 0, 0, 0, 0};
   return m > 128 ? launch_gemm<2, kModeWorkspace>(a, w, p, s) : launch_gemm<1, kModeWorkspace>(a, w, p, s);
 }
 
@@ -485,7 +481,7 @@ int ci8_channel_mm(const int8_t* a, const uint8_t* w, const float* a_scale, cons
     return launch_decode<true>(a, w, p, 0, s);
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, k, 1, 0, 0, 0, 0, 0, 1, 0};
+               m, n, k, 1, 0, 0, 0, 0, 0, 0};
   return launch_gemm<1, kModeBiased>(a, w, p, s);
 }
 
@@ -543,7 +539,7 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
       static_cast<long long>(m) * n > INT32_MAX || !aligned(codes, 16) || !aligned(w, 16))
     return kInvalid;
   GemmParams p{scales, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
-               m, n, 4096, groups, 0, 0, 0, 0, 0, 1, 0};
+               m, n, 4096, groups, 0, 0, 0, 0, 0, 0};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return m > 128 ? launch_gemm<2, kModeGrouped>(codes, w, p, s) : launch_gemm<1, kModeGrouped>(codes, w, p, s);
 }
@@ -565,7 +561,7 @@ int ci8_fused_channel_mm_gather(const int8_t* a, const int8_t* w, const float* a
     outputs[d] = static_cast<char*>(base) + block_bytes * rank;
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(outputs[0]), nullptr,
-               m, n_shard, k, 1, 0, 0, 0, 0, 0, 1, 0};
+               m, n_shard, k, 1, 0, 0, 0, 0, 0, 0};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const bool pair = schedule == 0 ? m > 128 : (schedule % 2 == 0);
   return pair ? launch_gemm<2, kModeFused>(a, w, p, s, outputs, world)

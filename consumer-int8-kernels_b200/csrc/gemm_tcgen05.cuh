@@ -49,9 +49,9 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int group_m;                // row tiles per raster group (L2 reuse of the A rows)
   int num_outputs;            // TMA-store destinations in OutputMaps; 0 selects direct stores
-  int full_tiles;             // work items [0, full_tiles) are whole tiles (complete waves)
-  int split;                  // each remaining tile is cut into `split` column slices (1, 2 or 4)
-  int total_items;            // full_tiles + (tiles - full_tiles) * split
+  int tile_n;                 // output channels per tile: 256, or narrower (a multiple of 32) when that
+                              // packs the tiles into fewer, fuller waves; 240 for the biased form
+  int stage_tx;               // bytes one CTA's TMA loads deliver per stage (A box + W box)
 };
 
 // Tensor maps of the output destinations: BF16 [M,N] matrices, boxes of 64 columns x 32 rows.
@@ -71,7 +71,6 @@ struct GemmConfig {
   static constexpr int kABytes = kBlockM * kBlockK;
   static constexpr int kBBytes = kBRowsSmem * kBlockK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStageTx = kABytes + kBRowsLoad * kBlockK;
   static constexpr int kStages = kCtas == 1 ? 4 : 6;
   static constexpr int kEpiWarps = kMode == kModeGrouped ? 8 : 4;
   static constexpr int kThreads = (2 + kEpiWarps) * 32;
@@ -88,20 +87,7 @@ struct GemmConfig {
 // Tile order: row tiles are walked in groups of group_m; inside a group the row tile index runs
 // fastest, then the channel tile. One wave of CTAs then touches a bounded set of A rows (which
 // stay in L2 while the weights stream past) instead of every row of a tall A.
-// Work items: the tiles of the complete waves are whole; the tiles of the last, partial wave are
-// cut into `split` column slices of 256/split accumulator columns so that they spread over the
-// idle CTAs (item -> tile, first column n_off and width n_width inside the tile).
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int item, int& mt, int& nt, int& n_off,
-                                            int& n_width) {
-  int tile = item;
-  n_off = 0;
-  n_width = 256;
-  if (item >= p.full_tiles) {
-    const int extra = item - p.full_tiles;
-    tile = p.full_tiles + extra / p.split;
-    n_width = 256 / p.split;
-    n_off = (extra % p.split) * n_width;
-  }
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mt, int& nt) {
   const int per_group = p.group_m * p.tiles_n;
   const int group = tile / per_group;
   const int within = tile - group * per_group;
@@ -185,7 +171,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;   // per group
-  const int total_tiles = p.total_items;   // work items (whole tiles, then column slices)
+  const int total_tiles = p.tiles_m * p.tiles_n;
+  // accumulator columns the MMA produces per tile (the biased form adds its 16 ones columns)
+  const int mma_n = kMode == kModeBiased ? Cfg::kTileN : p.tile_n;
   const int first_tile = kCtas == 2 ? (blockIdx.x >> 1) : blockIdx.x;
   const int tile_stride = kCtas == 2 ? (gridDim.x >> 1) : gridDim.x;
 
@@ -197,16 +185,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t leader_full0 = kCtas == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
       bool ok = true;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-        int mt, nt, n_off, n_width;
-        tile_coords(p, tile, mt, nt, n_off, n_width);
+        int mt, nt;
+        tile_coords(p, tile, mt, nt);
         const int a_row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM;
-        // each CTA of a pair supplies half of the slice's weight rows (the box still loads
-        // kBRowsSmem rows; the MMA reads only the first n_width / kCtas of them)
-        const int w_row = nt * Cfg::kChannelsPerTile + n_off + rank * (n_width / kCtas);
+        const int w_row = nt * p.tile_n + rank * (p.tile_n / kCtas);   // a pair's CTAs supply half the rows each
         for (int g = 0; ok && g < p.groups; ++g) {
           for (int kb = 0; kb < num_kb; ++kb) {
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-            if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageTx * kCtas);
+            if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), p.stage_tx * kCtas);
             const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
             const uint32_t b_dst = a_dst + Cfg::kABytes;
             const uint32_t bar = leader_full0 + 8u * stage;
@@ -231,9 +217,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       uint32_t phase = 0, acc_iter = 0;
       bool ok = true;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-        int mt, nt, n_off, n_width;
-        tile_coords(p, tile, mt, nt, n_off, n_width);
-        const uint32_t idesc = idesc_i8(Cfg::kBlockM * kCtas, n_width, /*b_unsigned=*/kMode == kModeBiased);
+        const uint32_t idesc = idesc_i8(Cfg::kBlockM * kCtas, mma_n, /*b_unsigned=*/kMode == kModeBiased);
         for (int g = 0; ok && g < p.groups; ++g, ++acc_iter) {
           const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
           if (!mbar_wait<kCtas == 2>(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
@@ -281,11 +265,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     bool ok = true;
     float total[kMode == kModeGrouped ? Cfg::kColsPerEpiWarp : 1];
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-      int mt, nt, n_off, n_width;
-      tile_coords(p, tile, mt, nt, n_off, n_width);
+      int mt, nt;
+      tile_coords(p, tile, mt, nt);
       const int row0 = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM + quarter * 32;
       const int row = row0 + lane;
-      const int n0 = nt * Cfg::kChannelsPerTile + n_off;   // first output column of this item
+      const int n0 = nt * p.tile_n;                       // first output column of this tile
       for (int g = 0; g < p.groups; ++g, ++acc_iter) {
         const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
         if (!mbar_wait<kCtas == 2>(tmem_full_bar(buf), acc_phase, abort_flag)) { ok = false; break; }
@@ -297,18 +281,22 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
         if constexpr (kMode == kModeBiased) {
           uint32_t ones[16];
           tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                            buf * Cfg::kTileN + Cfg::kChannelsPerTile, ones);
+                            buf * Cfg::kTileN + p.tile_n, ones);
           tmem_ld_wait();
           bias = static_cast<int32_t>(ones[0]) * 128;
         }
         const bool last_group = g + 1 == p.groups;
 #pragma unroll
         for (int chunk = 0; chunk < kChunks; ++chunk) {
-          if (col_base + chunk * 64 >= n_width) continue;  // a column slice is narrower than the tile
-          const int c0 = n0 + col_base + chunk * 64;      // first output column of this 64-wide box
+          const int tile_col = col_base + chunk * 64;     // first accumulator column of this 64-wide box
+          if (tile_col >= mma_n) continue;                // a narrow tile has fewer boxes
+          const int c0 = n0 + tile_col;                   // its first output column
           const bool store_box = (kMode != kModeGrouped || last_group) && c0 < p.n;
+          // a box that straddles the tile's right edge (tile_n is a multiple of 32, not of 64) must not
+          // be written as a whole 64-wide TMA box: its valid half goes out with direct stores
+          const bool tma_box = tma_out && tile_col + 64 <= p.tile_n;
           uint8_t* box = my_staging + (store_iter % Cfg::kStoreBufs) * Cfg::kStoreBoxBytes;
-          if (tma_out && store_box && store_iter >= Cfg::kStoreBufs) {
+          if (tma_box && store_box && store_iter >= Cfg::kStoreBufs) {
             // the box is reused only after its previous stores have finished reading it
             if (lane == 0) tma_store_wait_read<Cfg::kStoreBufs - 1>();
             __syncwarp();
@@ -327,11 +315,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
                 total[t] = g == 0 ? term : __fadd_rn(total[t], term);
               }
             }
-            if (!store_box || h0 >= p.n) continue;
+            if (!store_box || h0 >= p.n || tile_col + half * 32 >= p.tile_n) continue;
             // channel scales of these 32 columns: lane j holds sw[h0 + j]
             const float my_sw = (h0 + lane < p.n) ? __bfloat162float(p.sw[h0 + lane]) : 0.f;
             const int limit = kMode == kModeBiased
-                                  ? min(p.n - h0, Cfg::kChannelsPerTile - (col_base + chunk * 64 + half * 32))
+                                  ? min(p.n - h0, p.tile_n - (tile_col + half * 32))
                                   : p.n - h0;
             if constexpr (kMode == kModeBiased) {
 #pragma unroll
@@ -365,7 +353,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
               }
               packed[j >> 1] = pack_bf16x2(__fmul_rn(f0, s0), __fmul_rn(f1, s1));
             }
-            if (tma_out) {
+            if (tma_box) {
               // Stage with the 128-byte swizzle the store's tensor map expects: 16-byte chunk c of
               // box row r lives at chunk c ^ (r & 7).
               uint4* row_base = reinterpret_cast<uint4*>(box + lane * 128);
@@ -389,7 +377,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
               }
             }
           }
-          if (tma_out && store_box) {
+          if (tma_box && store_box) {
             // one lane stores the staged box to every destination (columns past N and rows past M
             // are clipped by the tensor map)
             fence_proxy_async_smem();

@@ -115,7 +115,9 @@ def linear_kat() -> dict:
 
 
 def main() -> None:
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference")
+    root = Path(sys.argv[1])
     (HERE / "weight_encoding.json").write_text(json.dumps(weight_encoding(root), indent=1) + "\n")
     (HERE / "activation_kat.json").write_text(json.dumps(activation_kat(), indent=1) + "\n")
     (HERE / "linear_kat.json").write_text(json.dumps(linear_kat(), indent=1) + "\n")

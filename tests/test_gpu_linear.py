@@ -95,12 +95,12 @@ def test_gemm_schedules_match_integer_products_and_capture(ops, m, fused, n, k):
 # more tiles than SMs, several K stages around the ring.
 TILE_CASES = [(128, 256, 128), (129, 260, 160), (255, 508, 96), (300, 1000, 1056), (513, 4, 32),
               (777, 2052, 4096), (4096, 512, 256), (100, 40000, 64), (3000, 3000, 3008),
-              # more tiles than CTAs with a small last wave: its tiles are cut into 2 or 4 column slices
+              # more tiles than CTAs with a small last wave: schedule 0 picks a narrower tile there
               (2048, 7168, 256), (2048, 7136, 160), (4096, 5120, 256), (1300, 30000, 96)]
 
 
 @pytest.mark.parametrize("m,n,k", TILE_CASES)
-@pytest.mark.parametrize("schedule", [1, 2, 3, 4])
+@pytest.mark.parametrize("schedule", [0, 1, 2, 3, 4, 5, 6])
 def test_fused_channel_mm_tile_and_k_tails(ops, m, n, k, schedule):
     a, w, sa, sw = linear_case(m, n, k, seed=m + n + k)
     out, check = guarded((m, n), torch.bfloat16, float("nan"))
