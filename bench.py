@@ -387,7 +387,32 @@ def other_configs(ops, workloads, device, peaks):
                                        channel_mm_u8_us=ms_u8 * 1e3, with_quantize_us=ms_q * 1e3,
                                        channel_gemv_us=ms_gemv * 1e3,
                                        channel_gemv_gbs=(n * k + 2 * n + 2 * m * k + 2 * m * n) / ms_gemv / 1e6)
+    # rows between the decode kernel (M <= 16) and a full tile: weight-stream bound on the tcgen05 GEMM
+    for m in (32, 64, 128):
+        x = workloads.activations(m, k, gen).to(device)
+        codes = torch.empty(m, k, dtype=torch.int8, device=device)
+        scales = torch.empty(m, device=device)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+        ops.quantize_rows(x, codes, scales)
+        nbytes = n * k + 2 * n + m * k + 4 * m + 2 * m * n
+        ms = _time_graph(lambda i: ops.fused_channel_mm(codes, copies[i % 4], scales, sw, out, 0), 40)
+        results[f"small_prefill_m{m}"] = dict(us=ms * 1e3, gbs=nbytes / ms / 1e6, frac_hbm=nbytes / ms / 1e6 / hbm)
     del copies, copies_u8
+    # decode on the down-projection shape (few channels, long K: the split-K cluster path)
+    n2, k2 = 5120, 17408
+    w2, w2_scale = workloads.weights(n2, k2, gen)
+    copies2 = [w2.to(device) for _ in range(4)]
+    sw2 = w2_scale.to(device)
+    for m in (1, 16):
+        x = workloads.activations(m, k2, gen).to(device)
+        codes = torch.empty(m, k2, dtype=torch.int8, device=device)
+        scales = torch.empty(m, device=device)
+        out = torch.empty(m, n2, dtype=torch.bfloat16, device=device)
+        ops.quantize_rows(x, codes, scales)
+        nbytes = n2 * k2 + 2 * n2 + m * k2 + 4 * m + 2 * m * n2
+        ms = _time_graph(lambda i: ops.fused_channel_mm(codes, copies2[i % 4], scales, sw2, out, 0), 40)
+        results[f"decode_down_m{m}"] = dict(us=ms * 1e3, gbs=nbytes / ms / 1e6, frac_hbm=nbytes / ms / 1e6 / hbm)
+    del copies2
     for name in ("prefill_gate_up", "prefill_down"):
         spec = WORKLOADS[name]
         m, n, k = spec["m"], spec["n"], spec["k"]

@@ -188,21 +188,31 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
 }
 
 // ------------------------------------------------------------------ decode (M <= 16) launch
-// Picks the split-K factor and the slab width (channels per CTA) that minimise the bytes the
-// busiest SM has to stream: waves * slab * K / split.
+// Picks the split-K factor and the slab width (channels per CTA, a multiple of 16: kind::i8 takes N in
+// steps of 16 above 32) from a small time model fitted to measurements on B200, in microseconds:
+//   fixed(split) + 4 (waves - 1) + max(weight bytes / HBM rate, waves * K blocks per CTA * time per ring stage)
+// where a ring stage (slab x 128 weight bytes + the 2 KB activation tile) takes at least 0.17 us
+// (barrier round trip, TMA and MMA issue) and one SM pulls at most about 75 GB/s. Split-K shortens the
+// per-CTA stream but costs a cluster launch and the shared-memory reduction. Clusters of four lose
+// a few SMs to placement (a cluster sits inside one GPC). Ties go to the smaller split and slab.
 void choose_decode_shape(int n, int k, int sms, int* split_out, int* slab_out) {
   const int num_kb = (k + 127) / 128;
+  const double hbm_us = static_cast<double>(n) * k / 6.4e6;
   double best = 1e300;
   int best_split = 1, best_slab = 128;
   for (int split = 1; split <= 4; split *= 2) {
     if (split > num_kb) break;
-    for (int slab = 128; slab <= 256; slab += 16) {
+    const long long capacity = split == 4 ? (sms / 4 - 4) * 4 : split == 2 ? (sms / 2) * 2 : sms;
+    const double fixed_us = split == 1 ? 4.5 : split == 2 ? 5.0 : 5.8;
+    for (int slab = 16; slab <= 256; slab += 16) {
       const long long slabs = (n + slab - 1) / slab;
       const long long ctas = slabs * split;
-      const long long waves = (ctas + sms - 1) / sms;
-      // a small per-CTA constant keeps needless splits from winning ties
-      const double cost = static_cast<double>(waves) * (static_cast<double>(slab) * ((num_kb + split - 1) / split) + 64.0 * split);
-      if (cost < best) { best = cost; best_split = split; best_slab = slab; }
+      const long long waves = (ctas + capacity - 1) / capacity;
+      const double stage_bytes = slab * 128.0 + 2048.0;
+      const double stage_us = stage_bytes / 75e3 > 0.17 ? stage_bytes / 75e3 : 0.17;
+      const double stream_us = static_cast<double>(waves) * ((num_kb + split - 1) / split) * stage_us;
+      const double cost = fixed_us + 4.0 * (waves - 1) + (stream_us > hbm_us ? stream_us : hbm_us);
+      if (cost < best * 0.995) { best = cost; best_split = split; best_slab = slab; }
     }
   }
   *split_out = best_split;
@@ -223,18 +233,23 @@ cudaError_t launch_decode_variant(const void* a, const void* w, const DecodePara
   if (err != cudaSuccess) return err;
   const int slabs = (p.n + p.slab - 1) / p.slab;
   cudaLaunchConfig_t config = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   config.gridDim = dim3(static_cast<unsigned>(slabs * kSplit));
   config.blockDim = dim3(Cfg::kThreads);
   config.dynamicSmemBytes = Cfg::kSmemBytes;
   config.stream = stream;
+  // the kernel's prologue (barriers, TMEM, descriptor prefetch) may overlap the tail of the kernel
+  // before it in the stream; it calls griddepcontrol.wait before touching global memory
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
   if (kSplit > 1) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = kSplit;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    config.attrs = attr;
-    config.numAttrs = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = kSplit;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    config.numAttrs = 2;
   }
   return cudaLaunchKernelEx(&config, kernel, map_w, map_a, p);
 }
@@ -247,9 +262,10 @@ cudaError_t launch_decode(const void* a, const void* w, DecodeParams p, int forc
     split = forced_split;
     const int per = sm_count() / split > 0 ? sm_count() / split : 1;
     slab = ((p.n + per - 1) / per + 15) / 16 * 16;
-    if (slab < 128) slab = 128;
+    if (slab < 16) slab = 16;
     if (slab > 256) slab = 256;
   }
+  if (slab < 16 || slab > 256 || slab % 16 != 0) return cudaErrorInvalidValue;   // not an instruction shape
   p.slab = slab;
   switch (split) {
     case 1: return launch_decode_variant<1, kBiased>(a, w, p, stream);

@@ -1,18 +1,33 @@
 // Small-M (<= 16 rows) W8A8 linear for decode: an HBM-streaming kernel.
 //
-// The weight matrix W [N,K] is read exactly once. The roles of the MMA operands are swapped
-// with respect to the prefill GEMM: a slab of up to 256 output channels is the M side of
-// tcgen05.mma (two M=128 instructions over rows [0,128) and [C-128,C) of the slab), and the
-// (zero-padded) 16 activation rows are the N side, so the accumulator in TMEM is
-// [channel, row] and 32 TMEM columns suffice. One CTA streams one slab through a deep TMA ring;
-// the slab width C is chosen on the host so that the slabs fill the SMs in one wave.
+// The weight matrix W [N,K] is read exactly once. One CTA owns a slab of C <= 256 output channels
+// (a multiple of 16) and streams it through a deep TMA ring; the host chooses C and the split-K
+// factor so that the CTAs fill the SMs in one wave. Per 128-byte K block a ring stage holds the
+// C x 128 weight tile and the 16 x 128 tile of (zero-padded) activation rows. The MMA is
+// tcgen05.mma kind::i8 with M = 64, N = C: the activations are the M side — only accumulator rows
+// 0..15 mean anything; rows 16..63 of the A operand are whatever shared memory follows the 2 KB
+// activation tile (integer garbage that lands in accumulator rows nobody reads) — and the weights
+// are the N side. Measured on B200, one such instruction (K = 32) takes about 24-33 cycles for
+// N <= 64 and N/2 cycles from N = 128 up, so four of them per stage stay far below the time the
+// stage's bytes take to arrive.
 //
-// Split-K: a cluster of kSplit CTAs shares a slab, each streaming its own K range; the
-// non-leader CTAs push their INT32 partials into the leader's shared memory (DSMEM) and the
-// leader adds them — integer addition, so the result does not depend on the split.
+// Warp roles: warp 2 issues the TMA loads, warp 1 the MMAs, warps 0 and 4 run the epilogue
+// (accumulator rows 0..15 are TMEM lanes 0..15, which only warps 0 and 4 can read). The producer
+// and MMA loops are executed by their whole warp with one elected lane issuing: the loop state
+// then lives in uniform registers, which is where TMA and MMA instructions take their operands;
+// issued from a single thread inside a divergent branch every instruction paid tens of cycles of
+// register moves, which capped a stage at about 0.3 us however narrow the slab.
+//
+// Split-K: a cluster of kSplit CTAs shares a slab, each streaming its own K range; the non-leader
+// CTAs push their INT32 partials into the leader's shared memory (DSMEM) and the leader adds them —
+// integer addition, so the result does not depend on the split.
 //
 // UINT8 weights (code+128): the MMA reads them as unsigned, and the epilogue removes
 // 128 * sum_k a[row,k], computed by the epilogue warps from the INT8 activations.
+//
+// The kernel is launched with programmatic stream serialization: its prologue may overlap the
+// tail of the kernel before it in the stream, and griddepcontrol.wait stands before the first
+// access to global memory.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -27,26 +42,33 @@ struct DecodeParams {
   __nv_bfloat16* out;         // [M,N]
   int32_t* workspace;         // optional [M,N] INT32 accumulators
   int m, n, k;
-  int slab;                   // channels per CTA (multiple of 16, 128..256)
+  int slab;                   // channels per CTA (multiple of 16, 16..256)
 };
 
 template <int kSplit>
 struct DecodeConfig {
-  static constexpr int kRows = 16;                       // padded activation rows (MMA N)
+  static constexpr int kRows = 16;                       // activation rows per tile (M <= 16)
   static constexpr int kBlockK = 128;
   static constexpr int kMaxSlab = 256;
-  static constexpr int kWBytes = kMaxSlab * kBlockK;     // 32 KB
-  static constexpr int kABytes = kRows * kBlockK;        // 2 KB
-  static constexpr int kStageBytes = kWBytes + kABytes;
-  static constexpr int kStages = kSplit == 1 ? 6 : 5;
-  static constexpr int kReduceBytes = kSplit == 1 ? 0 : (kSplit - 1) * 2 * 128 * kRows * 4;
-  static constexpr int kThreads = 192;
-  static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kReduceBytes + kBarrierBytes + 1024;
+  static constexpr int kABytes = kRows * kBlockK;        // 2 KB actually loaded per stage
+  static constexpr int kMmaM = 64;                       // smallest M of the instruction
+  static constexpr int kAOperandBytes = kMmaM * kBlockK; // what the instruction reads from the tile's start on
+  // The ring is a fixed region cut into stages of slab*128 + 2 KB bytes, as many as fit (at most
+  // kMaxStages): a narrow slab gets more, smaller stages, so the bytes in flight stay the same.
+  static constexpr int kRingBytes = (kSplit == 1 ? 6 : kSplit == 2 ? 5 : 4) * (kMaxSlab * kBlockK + kABytes);
+  static constexpr int kMaxStages = 24;
+  static constexpr int kReduceBytes = kSplit == 1 ? 0 : (kSplit - 1) * kRows * kMaxSlab * 4;
+  static constexpr int kTmemColumns = 256;
+  static constexpr int kThreads = 160;                   // warps 0 and 4 epilogue, 1 MMA, 2 TMA, 3 idle
+  static constexpr int kBarrierBytes = 512;
+  static constexpr int kScaleBytes = kMaxSlab * 4 + 2 * kRows * 4;   // FP32 channel scales of the slab + row sums
+  // the last stage's A operand extends kAOperandBytes past its tile: keep that inside the allocation
+  static constexpr int kSmemBytes = kRingBytes + kAOperandBytes + kReduceBytes + kBarrierBytes + kScaleBytes + 1024;
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
 template <int kSplit, bool kBiased>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(160, 1)
 decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_a, const DecodeParams p) {
   using Cfg = DecodeConfig<kSplit>;
@@ -55,27 +77,31 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
   const uint32_t smem_base = raw_addr + pad;
-  int32_t* reduce_buf = reinterpret_cast<int32_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
-  uint8_t* bar_region = smem + Cfg::kStages * Cfg::kStageBytes + Cfg::kReduceBytes;
-  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes + Cfg::kReduceBytes;
+  constexpr int kReduceOffset = Cfg::kRingBytes + Cfg::kAOperandBytes;
+  int32_t* reduce_buf = reinterpret_cast<int32_t*>(smem + kReduceOffset);   // [rank-1][kMaxSlab][16]: lanes (rows) adjacent
+  uint8_t* bar_region = smem + kReduceOffset + Cfg::kReduceBytes;
+  const uint32_t bar_base = smem_base + kReduceOffset + Cfg::kReduceBytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
-  const uint32_t done_bar = bar_base + 8u * (2 * Cfg::kStages);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_region + 8 * (2 * Cfg::kStages + 1));
+  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kMaxStages + s); };
+  const uint32_t done_bar = bar_base + 8u * (2 * Cfg::kMaxStages);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_region + 8 * (2 * Cfg::kMaxStages + 1));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int32_t* row_sums = reinterpret_cast<int32_t*>(tmem_slot + 2);   // [16]
+  float* scale_tab = reinterpret_cast<float*>(bar_region + Cfg::kBarrierBytes);          // [kMaxSlab]
+  int32_t* row_sums = reinterpret_cast<int32_t*>(scale_tab + Cfg::kMaxSlab);             // [2][16]
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const uint32_t rank = kSplit > 1 ? cluster_ctarank() : 0u;
   const int slab_index = blockIdx.x / kSplit;
   const int n0 = slab_index * p.slab;
   const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;
   const int kb_begin = static_cast<int>((static_cast<long long>(num_kb) * rank) / kSplit);
   const int kb_end = static_cast<int>((static_cast<long long>(num_kb) * (rank + 1)) / kSplit);
-  const bool second_half = p.slab > 128;
+  const int w_bytes = p.slab * Cfg::kBlockK;                 // weight tile of one stage (multiple of 1024)
+  const int stage_bytes = w_bytes + Cfg::kABytes;
+  const int num_stages = min(Cfg::kMaxStages, Cfg::kRingBytes / stage_bytes);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::kStages; ++s) {
+    for (int s = 0; s < num_stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
@@ -86,158 +112,215 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     prefetch_tensormap(&map_a);
   }
   if (warp == 1) {
-    tmem_alloc<1>(smem_u32(tmem_slot), 32);
+    tmem_alloc<1>(smem_u32(tmem_slot), Cfg::kTmemColumns);
     tmem_relinquish<1>();
   }
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched only shared memory, TMEM and kernel parameters; from here on global
+  // memory is read and written, so the previous kernel in the stream must have finished.
+  pdl_launch_dependents();
+  pdl_wait();
 
-  if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      const uint32_t tx = static_cast<uint32_t>(p.slab) * Cfg::kBlockK + Cfg::kABytes;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
-        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
-          __nanosleep(200000);
-          break;
-        }
-        mbar_arrive_expect_tx(full_bar(stage), tx);
-        const uint32_t w_dst = smem_base + stage * Cfg::kStageBytes;
-        tma_load_2d(w_dst, &map_w, kb * Cfg::kBlockK, n0, full_bar(stage));
-        tma_load_2d(w_dst + Cfg::kWBytes, &map_a, kb * Cfg::kBlockK, 0, full_bar(stage));
-        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+  if (warp == 2) {
+    // ---------------------------------------------------------------- TMA producer
+    // The whole warp runs the loop and an elected lane issues: loop state then stays in uniform
+    // registers, which is where the TMA and MMA instructions take their operands from (issued
+    // from one thread of a divergent branch they cost tens of cycles each in register moves).
+    int stage = 0;
+    uint32_t phase = 0;
+    const uint32_t tx = static_cast<uint32_t>(stage_bytes);
+    // Every slab walks its K range from a different starting block (integer accumulation does
+    // not care about the order), which spreads the CTAs over the activation lines and DRAM pages.
+    const int count = kb_end - kb_begin;
+    int kb = count > 0 ? kb_begin + (slab_index * 5) % count : kb_begin;
+    for (int i = 0; i < count; ++i) {
+      if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) {
+        __nanosleep(200000);
+        break;
       }
+      if (elect_one()) {
+        mbar_arrive_expect_tx(full_bar(stage), tx);
+        const uint32_t w_dst = smem_base + stage * stage_bytes;
+        tma_load_2d(w_dst, &map_w, kb * Cfg::kBlockK, n0, full_bar(stage));
+        tma_load_2d(w_dst + w_bytes, &map_a, kb * Cfg::kBlockK, 0, full_bar(stage));
+      }
+      __syncwarp();
+      if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+      if (++kb == kb_end) kb = kb_begin;
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // "A" operand = weights (unsigned when biased), "B" operand = activations (signed).
-      constexpr uint32_t kIdesc = idesc_i8(128, Cfg::kRows, /*b_unsigned=*/false, /*a_unsigned=*/kBiased);
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
-        if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
-        tcgen05_fence_after();
-        const uint32_t w_addr = smem_base + stage * Cfg::kStageBytes;
-        const uint64_t w_desc0 = smem_desc_sw128(w_addr);
-        const uint64_t w_desc1 = smem_desc_sw128(w_addr + (p.slab - 128) * Cfg::kBlockK);
-        const uint64_t a_desc = smem_desc_sw128(w_addr + Cfg::kWBytes);
-        const uint32_t first = kb == kb_begin ? 0u : 1u;
+    // ---------------------------------------------------------------- MMA issuer
+    // A = activations (signed, M = 64 of which 16 rows are real), B = weights (N = slab)
+    const uint32_t idesc = idesc_i8(Cfg::kMmaM, p.slab, /*b_unsigned=*/kBiased);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int kb = kb_begin; kb < kb_end; ++kb) {
+      if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag))) { ok = false; break; }
+      tcgen05_fence_after();
+      const uint32_t w_addr = smem_base + stage * stage_bytes;
+      const uint64_t w_desc = smem_desc_sw128(w_addr);
+      const uint64_t a_desc = smem_desc_sw128(w_addr + w_bytes);
+      if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          mma_i8<1>(tmem_base, w_desc0 + 2u * ks, a_desc + 2u * ks, kIdesc, first | (ks != 0));
-          if (second_half)
-            mma_i8<1>(tmem_base + Cfg::kRows, w_desc1 + 2u * ks, a_desc + 2u * ks, kIdesc,
-                      first | (ks != 0));
-        }
+        for (int ks = 0; ks < 4; ++ks)
+          mma_i8<1>(tmem_base, a_desc + 2u * ks, w_desc + 2u * ks, idesc, (kb != kb_begin || ks != 0) ? 1u : 0u);
         mma_commit(empty_bar(stage));
-        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
       }
-      if (ok) mma_commit(done_bar);
+      __syncwarp();
+      if (++stage == num_stages) { stage = 0; phase ^= 1u; }
     }
-  } else {
-    // -------------------------------------------------------------- epilogue warps (128 threads)
-    const int t = threadIdx.x - 64;              // 0..127
-    const int quarter = warp & 3;                // TMEM lane quarter of this warp
-    const int tmem_lane = quarter * 32 + lane;   // accumulator row = channel within the half
+    if (ok && elect_one()) mma_commit(done_bar);
+    __syncwarp();
+  } else if (warp == 0 || warp == 4) {
+    // ---------------------------------------------------------------- epilogue warps
+    // Accumulator rows 0..15 live in TMEM lanes 0..15, which only warps 0 and 4 of the CTA can read
+    // (a warp reaches the lane quarter of its index modulo four). The two warps take alternate
+    // 32-channel chunks; lane = accumulator row = activation row, lanes 16..31 carry garbage rows.
+    const int e = warp >> 2;
+    const int row = lane;
+    constexpr int kMyChunks = Cfg::kMaxSlab / 64;
     if constexpr (kBiased) {
-      // sum_k a[row,k] over this CTA's K range: 8 threads per activation row.
-      const int row = t >> 3, part = t & 7;
+      // sum_k a[row,k] over this CTA's K range: two lanes per activation row (each warp its own copy)
+      const int r = lane >> 1, part = lane & 1;
       int sum = 0;
-      if (row < p.m) {
+      if (r < p.m) {
         const int k_begin = kb_begin * Cfg::kBlockK, k_end = min(kb_end * Cfg::kBlockK, p.k);
-        const int8_t* src = p.a + static_cast<size_t>(row) * p.k;
+        const int8_t* src = p.a + static_cast<size_t>(r) * p.k;
         if (reinterpret_cast<uintptr_t>(p.a) % 16 == 0 && p.k % 16 == 0) {
-          for (int k = k_begin + part * 16; k < k_end; k += 128) {
-            const uint4 v = *reinterpret_cast<const uint4*>(src + k);
+          for (int kk = k_begin + part * 16; kk < k_end; kk += 32) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src + kk);
             sum = __dp4a(static_cast<int>(v.x), 0x01010101, sum);
             sum = __dp4a(static_cast<int>(v.y), 0x01010101, sum);
             sum = __dp4a(static_cast<int>(v.z), 0x01010101, sum);
             sum = __dp4a(static_cast<int>(v.w), 0x01010101, sum);
           }
         } else {
-          for (int k = k_begin + part; k < k_end; k += 8) sum += src[k];
+          for (int kk = k_begin + part; kk < k_end; kk += 2) sum += src[kk];
         }
       }
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-      if (part == 0) row_sums[row] = sum;
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (part == 0) row_sums[e * Cfg::kRows + r] = sum;
     }
-    const bool ok = kb_end > kb_begin
-                        ? mbar_wait(done_bar, 0u, abort_flag)
-                        : true;
+    // the scales do not depend on the accumulation: fetch them while the weights stream
+    const int chunks = (p.slab + 31) / 32;
+    const float row_scale = row < p.m ? p.sa[row] : 0.f;
+#pragma unroll
+    for (int i = 0; i < kMyChunks; ++i) {
+      const int c = 2 * i + e;
+      const int channel = n0 + c * 32 + lane;
+      scale_tab[c * 32 + lane] = (c * 32 + lane < p.slab && channel < p.n) ? __bfloat162float(p.sw[channel]) : 0.f;
+    }
+    __syncwarp();
+    const bool have_work = kb_end > kb_begin;
+    const bool ok = have_work ? mbar_wait(done_bar, 0u, abort_flag) : true;
     tcgen05_fence_after();
-    int32_t acc[2][16];
+    const bool live = __all_sync(0xffffffffu, ok) && have_work;
+    const int32_t bias = (kBiased && row < Cfg::kRows) ? 128 * row_sums[e * Cfg::kRows + row] : 0;
+    const bool out_vec = (p.n % 8 == 0) && (reinterpret_cast<uintptr_t>(p.out) % 16 == 0);
+    const bool ws_vec = (p.n % 4 == 0) && (reinterpret_cast<uintptr_t>(p.workspace) % 16 == 0);
+
+    // Walks this warp's chunks with the TMEM read of the next chunk in flight while the current
+    // one is processed; f(chunk, acc) gets the bias-corrected INT32 accumulators of 32 channels.
+    auto for_each_chunk = [&](auto&& f) {
+      uint32_t v[2][32];
+      if (live && e < chunks) tmem_ld_32x32(tmem_base + e * 32, v[0]);
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      uint32_t v[16];
-      if (ok && kb_end > kb_begin && (h == 0 || second_half)) {
-        tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + h * Cfg::kRows, v);
-        tmem_ld_wait();
-      } else {
+      for (int i = 0; i < kMyChunks; ++i) {
+        const int chunk = 2 * i + e;
+        if (chunk >= chunks) break;
+        uint32_t (&cur)[32] = v[i & 1];
+        if (live) {
+          tmem_ld_wait_for(cur);
+        } else {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = 0u;
+          for (int j = 0; j < 32; ++j) cur[j] = 0u;
+        }
+        if (i + 1 < kMyChunks && live && chunk + 2 < chunks) tmem_ld_32x32(tmem_base + (chunk + 2) * 32, v[(i + 1) & 1]);
+        int32_t acc[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = static_cast<int32_t>(cur[j]) - bias;
+        f(chunk, acc);
       }
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        acc[h][j] = static_cast<int32_t>(v[j]);
-        if constexpr (kBiased) acc[h][j] -= 128 * row_sums[j];
-      }
-    }
+    };
+
     if constexpr (kSplit > 1) {
       if (rank != 0) {
-        // push partials into the leader's reduce buffer: [rank-1][half][row j][channel lane]
+        // push this CTA's partials into the leader's reduce buffer: [rank-1][channel][row]
         const uint32_t remote = map_to_cta(smem_u32(reduce_buf), 0);
+        for_each_chunk([&](int chunk, int32_t (&acc)[32]) {
+          if (row < Cfg::kRows) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const uint32_t offset = ((((rank - 1) * 2 + h) * 16 + j) * 128 + tmem_lane) * 4;
-            asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + offset), "r"(acc[h][j]) : "memory");
+            for (int j = 0; j < 32; ++j) {
+              const uint32_t offset = (((rank - 1) * Cfg::kMaxSlab + chunk * 32 + j) * Cfg::kRows + row) * 4;
+              asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + offset), "r"(acc[j]) : "memory");
+            }
           }
+        });
       }
-    }
-    if constexpr (kSplit > 1) {
       cluster_arrive();
       cluster_wait();
     }
     if (rank == 0) {
-      if constexpr (kSplit > 1) {
+      for_each_chunk([&](int chunk, int32_t (&acc)[32]) {
+        if constexpr (kSplit > 1) {
+          if (row < Cfg::kRows) {
 #pragma unroll
-        for (int r = 0; r < kSplit - 1; ++r)
+            for (int r = 0; r < kSplit - 1; ++r)
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              acc[h][j] += reduce_buf[((r * 2 + h) * 16 + j) * 128 + tmem_lane];
-      }
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        if (h == 1 && !second_half) break;
-        const int local = h == 0 ? tmem_lane : p.slab - 128 + tmem_lane;
-        if (h == 1 && local < 128) continue;        // already produced by the first half
-        const int channel = n0 + local;
-        if (local >= p.slab || channel >= p.n) continue;
-        const float channel_scale = __bfloat162float(p.sw[channel]);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (j < p.m) {
-            const float scaled = __fmul_rn(__int2float_rn(acc[h][j]), p.sa[j]);
-            p.out[static_cast<size_t>(j) * p.n + channel] =
-                __float2bfloat16_rn(__fmul_rn(scaled, channel_scale));
-            if (p.workspace) p.workspace[static_cast<size_t>(j) * p.n + channel] = acc[h][j];
+              for (int j = 0; j < 32; ++j) acc[j] += reduce_buf[(r * Cfg::kMaxSlab + chunk * 32 + j) * Cfg::kRows + row];
           }
         }
-      }
+        const int c0 = n0 + chunk * 32;                     // first output channel of this chunk
+        if (c0 >= p.n) return;
+        const int limit = min(min(32, p.slab - chunk * 32), p.n - c0);
+        const float4* scales = reinterpret_cast<const float4*>(scale_tab + chunk * 32);   // broadcast reads
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 s = scales[j >> 2];
+          const float f0 = __fmul_rn(__int2float_rn(acc[j]), row_scale);
+          const float f1 = __fmul_rn(__int2float_rn(acc[j + 1]), row_scale);
+          const float f2 = __fmul_rn(__int2float_rn(acc[j + 2]), row_scale);
+          const float f3 = __fmul_rn(__int2float_rn(acc[j + 3]), row_scale);
+          __nv_bfloat162 lo = __floats2bfloat162_rn(__fmul_rn(f0, s.x), __fmul_rn(f1, s.y));
+          __nv_bfloat162 hi = __floats2bfloat162_rn(__fmul_rn(f2, s.z), __fmul_rn(f3, s.w));
+          packed[j >> 1] = *reinterpret_cast<uint32_t*>(&lo);
+          packed[(j >> 1) + 1] = *reinterpret_cast<uint32_t*>(&hi);
+        }
+        if (row < p.m) {
+          __nv_bfloat16* dst = p.out + static_cast<size_t>(row) * p.n + c0;
+          if (out_vec && limit == 32) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+              *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (j < limit) {
+                const uint32_t word = packed[j >> 1];
+                reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>((j & 1) ? (word >> 16) : (word & 0xffffu));
+              }
+          }
+          if (p.workspace) {
+            int32_t* ws = p.workspace + static_cast<size_t>(row) * p.n + c0;
+            if (ws_vec && limit == 32) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<int4*>(ws + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (j < limit) ws[j] = acc[j];
+            }
+          }
+        }
+      });
     }
   }
   if constexpr (kSplit > 1) {
-    if (warp < 2) {   // the epilogue warps passed the cluster rendezvous above
+    if (warp != 0 && warp != 4) {   // the epilogue warps passed the cluster rendezvous above
       cluster_arrive();
       cluster_wait();
     }
@@ -246,7 +329,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    tmem_dealloc<1>(tmem_base, 32);
+    tmem_dealloc<1>(tmem_base, Cfg::kTmemColumns);
   }
 }
 
