@@ -125,7 +125,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_region + 8 * (2 * Cfg::kStages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
   const uint32_t rank = kCtas == 2 ? cluster_ctarank() : 0u;
 
@@ -179,19 +179,24 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      const uint32_t leader_full0 = kCtas == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
-      bool ok = true;
-      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-        int mt, nt;
-        tile_coords(p, tile, mt, nt);
-        const int a_row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM;
-        const int w_row = nt * p.tile_n + rank * (p.tile_n / kCtas);   // a pair's CTAs supply half the rows each
-        for (int g = 0; ok && g < p.groups; ++g) {
-          for (int kb = 0; kb < num_kb; ++kb) {
-            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+    // The producer and MMA loops are run by their whole warp with one elected lane issuing: the
+    // loop state then lives in uniform registers, which is where TMA and MMA instructions take
+    // their operands. Issued from a single thread inside a divergent branch, every instruction
+    // pays tens of cycles of register moves (measured: 47-76 cycles per MMA against 128 cycles
+    // of tensor-pipe time for a 128 x 256 x 32 step, before the waits and commits).
+    int stage = 0;
+    uint32_t phase = 0;
+    const uint32_t leader_full0 = kCtas == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
+    bool ok = true;
+    for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
+      int mt, nt;
+      tile_coords(p, tile, mt, nt);
+      const int a_row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM;
+      const int w_row = nt * p.tile_n + rank * (p.tile_n / kCtas);   // a pair's CTAs supply half the rows each
+      for (int g = 0; ok && g < p.groups; ++g) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) { ok = false; break; }
+          if (elect_one()) {
             if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), p.stage_tx * kCtas);
             const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
             const uint32_t b_dst = a_dst + Cfg::kABytes;
@@ -204,50 +209,57 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
               tma_load_2d(a_dst, &map_a, kx, g * p.m + a_row, bar);
               tma_load_2d(b_dst, &map_w, g * p.k + kx, w_row, bar);
             }
-            if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
           }
+          __syncwarp();
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
         }
       }
-      if (!ok) __nanosleep(200000);  // let loads already in flight land before teardown
     }
+    if (!ok) __nanosleep(200000);  // let loads already in flight land before teardown
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (rank == 0 && lane == 0) {
+    if (rank == 0) {
       int stage = 0;
       uint32_t phase = 0, acc_iter = 0;
       bool ok = true;
+      const uint32_t idesc = idesc_i8(Cfg::kBlockM * kCtas, mma_n, /*b_unsigned=*/kMode == kModeBiased);
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-        const uint32_t idesc = idesc_i8(Cfg::kBlockM * kCtas, mma_n, /*b_unsigned=*/kMode == kModeBiased);
         for (int g = 0; ok && g < p.groups; ++g, ++acc_iter) {
           const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
-          if (!mbar_wait<kCtas == 2>(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag))) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t tmem_d = tmem_base + buf * Cfg::kTileN;
           for (int kb = 0; kb < num_kb; ++kb) {
-            if (!mbar_wait<kCtas == 2>(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(full_bar(stage), phase, abort_flag))) { ok = false; break; }
             tcgen05_fence_after();
             const uint32_t a_addr = smem_base + stage * Cfg::kStageBytes;
             const uint64_t a_desc = smem_desc_sw128(a_addr);
             const uint64_t b_desc = smem_desc_sw128(a_addr + Cfg::kABytes);
+            if (elect_one()) {
 #pragma unroll
-            for (int ks = 0; ks < Cfg::kBlockK / 32; ++ks)
-              mma_i8<kCtas>(tmem_d, a_desc + 2u * ks, b_desc + 2u * ks, idesc,
-                            (kb | ks) != 0 ? 1u : 0u);
-            if constexpr (kCtas == 2) {
-              mma_commit_pair(map_to_cta(empty_bar(stage), 0));
-              mma_commit_pair(map_to_cta(empty_bar(stage), 1));
-            } else {
-              mma_commit(empty_bar(stage));
+              for (int ks = 0; ks < Cfg::kBlockK / 32; ++ks)
+                mma_i8<kCtas>(tmem_d, a_desc + 2u * ks, b_desc + 2u * ks, idesc,
+                              (kb | ks) != 0 ? 1u : 0u);
+              if constexpr (kCtas == 2) {
+                mma_commit_pair(map_to_cta(empty_bar(stage), 0));
+                mma_commit_pair(map_to_cta(empty_bar(stage), 1));
+              } else {
+                mma_commit(empty_bar(stage));
+              }
             }
+            __syncwarp();
             if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
           }
           if (!ok) break;
-          if constexpr (kCtas == 2) {
-            mma_commit_pair(map_to_cta(tmem_full_bar(buf), 0));
-            mma_commit_pair(map_to_cta(tmem_full_bar(buf), 1));
-          } else {
-            mma_commit(tmem_full_bar(buf));
+          if (elect_one()) {
+            if constexpr (kCtas == 2) {
+              mma_commit_pair(map_to_cta(tmem_full_bar(buf), 0));
+              mma_commit_pair(map_to_cta(tmem_full_bar(buf), 1));
+            } else {
+              mma_commit(tmem_full_bar(buf));
+            }
           }
+          __syncwarp();
         }
       }
     }
