@@ -168,16 +168,19 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
 
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   cudaLaunchConfig_t config = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
   if (kCtas == 2) {
     const long long clusters = tiles < sms / 2 ? tiles : sms / 2;
     config.gridDim = dim3(static_cast<unsigned>(2 * clusters));
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    config.attrs = attr;
-    config.numAttrs = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    config.numAttrs = 2;
   } else {
     config.gridDim = dim3(static_cast<unsigned>(tiles < sms ? tiles : sms));
   }
@@ -185,6 +188,25 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   config.dynamicSmemBytes = Cfg::kSmemBytes;
   config.stream = stream;
   return cudaLaunchKernelEx(&config, kernel, map_a, map_w, out_maps, p);
+}
+
+// Launch with programmatic stream serialization: the kernel may become resident while the kernel
+// before it in the stream drains; every kernel launched this way calls griddepcontrol.wait before
+// its first access to global memory.
+template <typename... Params, typename... Args>
+cudaError_t launch_serialized(void (*kernel)(Params...), unsigned grid, unsigned block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(block);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
 // ------------------------------------------------------------------ decode (M <= 16) launch
@@ -300,8 +322,9 @@ void launch_quantize_vec(const void* x, int8_t* q, float* s, int rows, int k, in
   }
   const int needed = (rows + kRowsPerCta - 1) / kRowsPerCta;
   constexpr bool kPersistent = !kSwiGLU && kPacks >= 4 && kPacks <= 9;
-  quantize_rows_vec_kernel<kTeam, kPacks, kSwiGLU><<<(!kPersistent || needed < per_device) ? needed : per_device, kThreads, 0, stream>>>(
-      static_cast<const uint16_t*>(x), q, s, rows, k, m, groups);
+  launch_serialized(quantize_rows_vec_kernel<kTeam, kPacks, kSwiGLU>,
+                    static_cast<unsigned>((!kPersistent || needed < per_device) ? needed : per_device), kThreads, 0,
+                    stream, static_cast<const uint16_t*>(x), q, s, rows, k, m, groups);
 }
 
 // rows = output rows; groups == 0 for the plain form.
@@ -526,9 +549,11 @@ int ci8_channel_gemv(const void* x, const int8_t* w, const void* w_scale, void* 
     const auto* sb = static_cast<const __nv_bfloat16*>(w_scale);
     auto* ob = static_cast<__nv_bfloat16*>(out);
     if (m <= 8)
-      gemv_w8a16_tma_kernel<1><<<ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s>>>(map_w, map_x, sb, ob, m, n, k, slab);
+      return launch_serialized(gemv_w8a16_tma_kernel<1>, ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s,
+                               map_w, map_x, sb, ob, m, n, k, slab);
     else
-      gemv_w8a16_tma_kernel<2><<<ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s>>>(map_w, map_x, sb, ob, m, n, k, slab);
+      return launch_serialized(gemv_w8a16_tma_kernel<2>, ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s,
+                               map_w, map_x, sb, ob, m, n, k, slab);
     return cudaGetLastError();
   }
   if (aligned(x, 16)) {

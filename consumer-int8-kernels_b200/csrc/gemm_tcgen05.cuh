@@ -169,6 +169,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   }
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Launched with programmatic stream serialization: everything above (barriers, TMEM, descriptor
+  // prefetch) may overlap the tail of the previous kernel in the stream; global memory is touched
+  // only after that kernel has finished.
+  pdl_wait();
 
   const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;   // per group
   const int total_tiles = p.tiles_m * p.tiles_n;
@@ -215,6 +219,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
     }
+    pdl_launch_dependents();       // all of this CTA's loads are issued: the next kernel may set up
     if (!ok) __nanosleep(200000);  // let loads already in flight land before teardown
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer

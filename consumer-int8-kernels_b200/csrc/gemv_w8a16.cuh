@@ -255,6 +255,10 @@ gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     prefetch_tensormap(&map_x);
   }
   __syncthreads();
+  // launched with programmatic stream serialization: the set-up above may overlap the previous
+  // kernel's tail; global memory is touched only after that kernel has finished
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == Cfg::kConsumerWarps) {
     // ---------------------------------------------------------------- producer

@@ -17,6 +17,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cstdint>
+#include "sm100_ptx.cuh"
 
 namespace ci8 {
 
@@ -129,6 +130,11 @@ quantize_rows_vec_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kRowsPerCta;
   const int packs_in_row = k >> 3;
   int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + threadIdx.x / kTeam;
+
+  // launched with programmatic stream serialization: the next kernel may start its prologue now,
+  // and nothing is read before the previous kernel in the stream has finished
+  pdl_launch_dependents();
+  pdl_wait();
 
   uint4 pack[kPacks];
   uint4 next[kPrefetch ? kPacks : 1];
