@@ -127,12 +127,27 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   const int sms = sm_count();
   const long long workers = kCtas == 2 ? sms / 2 : sms;
   p.tiles_m = (p.m + Cfg::kBlockM * kCtas - 1) / (Cfg::kBlockM * kCtas);
-  // Tile width: 256 accumulator columns unless a schedule asks for a narrower tile (a multiple of 32;
-  // schedules 3..6). Narrower tiles were tried as a cure for a mostly empty last wave (fewer, fuller
-  // waves on paper) and measured slower: a 224-wide MMA does not take less time than a 256-wide one.
-  // The biased form keeps 240 channels + 16 ones rows; the gathering form keeps 256.
-  int tile_n = kMode == kModeBiased ? Cfg::kChannelsPerTile : 256;
-  if (kMode != kModeBiased && num_outputs <= 1 && p.tile_n > 0) tile_n = p.tile_n;
+  // Tile width. The persistent grid works through the tiles in waves of `workers` equally long tiles,
+  // so the time is about waves x (tile width + a per-tile overhead worth ~9 columns); a narrower tile
+  // (224 or 192 accumulator columns) wins when it turns a mostly empty last wave into fuller ones. The
+  // 224-wide tile runs ~3 % below the line (its last 64-column box straddles the tile edge and leaves
+  // through direct stores). Ties go to the wider tile. A schedule can force the width; the biased
+  // form keeps 240 channels + 16 ones rows; the gathering form needs whole 64-column boxes (256 or 192).
+  int tile_n = 256;
+  if (kMode == kModeBiased) {
+    tile_n = Cfg::kChannelsPerTile;
+  } else if (p.tile_n > 0 && num_outputs <= 1) {
+    tile_n = p.tile_n;
+  } else {
+    double best = 1e300;
+    for (int cand = 256; cand >= 192; cand -= 32) {
+      if (cand % 64 != 0 && num_outputs > 1) continue;
+      const long long tiles = static_cast<long long>(p.tiles_m) * ((p.n + cand - 1) / cand);
+      const long long waves = (tiles + workers - 1) / workers;
+      const double cost = static_cast<double>(waves) * (cand + 9) * (cand == 224 ? 1.03 : 1.0);
+      if (cost < best * 0.999) { best = cost; tile_n = cand; }
+    }
+  }
   p.tile_n = tile_n;
   p.tiles_n = (p.n + tile_n - 1) / tile_n;
   const int w_box_rows = kMode == kModeBiased ? Cfg::kBRowsLoad : tile_n / kCtas;
@@ -485,7 +500,7 @@ int ci8_fused_channel_mm(const int8_t* a, const int8_t* w, const float* a_scale,
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
                m, n, k, 1, 0, 0, 0, 0, 0, 0};
-  // schedule 0: pairs of CTAs once there is more than one 128-row block, 256-wide tiles; odd values
+  // schedule 0: pairs of CTAs once there is more than one 128-row block, tile width chosen by launch_gemm; odd values
   // force the single-CTA tile, even values the two-CTA tile; 1/2 with 256-wide tiles, 3/4 with
   // 224-wide, 5/6 with 192-wide tiles. All give identical bits.
   const bool pair = schedule == 0 ? m > 128 : (schedule % 2 == 0);
