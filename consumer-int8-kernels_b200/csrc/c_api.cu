@@ -127,29 +127,45 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   const int sms = sm_count();
   const long long workers = kCtas == 2 ? sms / 2 : sms;
   p.tiles_m = (p.m + Cfg::kBlockM * kCtas - 1) / (Cfg::kBlockM * kCtas);
-  // Tile width. The persistent grid works through the tiles in waves of `workers` equally long tiles,
-  // so the time is about waves x (tile width + a per-tile overhead worth ~9 columns); a narrower tile
-  // (224 or 192 accumulator columns) wins when it turns a mostly empty last wave into fuller ones. The
-  // 224-wide tile runs ~3 % below the line (its last 64-column box straddles the tile edge and leaves
-  // through direct stores). Ties go to the wider tile. A schedule can force the width; the biased
-  // form keeps 240 channels + 16 ones rows; the gathering form needs whole 64-column boxes (256 or 192).
-  int tile_n = 256;
+  // Tile width and last-wave slicing. The persistent grid works through the tiles in waves of `workers`
+  // equally long tiles, so the time is about waves x (tile width + a per-tile overhead worth ~9 columns).
+  // Two remedies for a mostly empty last wave, both chosen here from that model: a narrower tile (224 or
+  // 192 accumulator columns) that packs the work into fuller waves, and cutting the last wave's tiles
+  // into 2 or 4 column slices when those fit into one pass over the workers (measured: a half slice lasts
+  // ~0.6 and a quarter slice ~0.5 of a whole tile, ~0.8 in the grouped form: the MMAs take about N/2 cycles
+  // but the slice still streams all of A through a ring sized for whole tiles).
+  // The 224-wide tile runs ~3 % below the line (its last 64-column box straddles the tile edge and
+  // leaves through direct stores) and cannot be sliced (112 is not a multiple of 32). Ties go to the
+  // wider tile. A schedule can force the width; the biased form keeps 240 channels + 16 ones rows,
+  // unsliced; the gathering form needs whole 64-column boxes (256 or 192 wide, slices of 128 or 64).
+  int tile_n = 256, split = 1;
   if (kMode == kModeBiased) {
     tile_n = Cfg::kChannelsPerTile;
-  } else if (p.tile_n > 0 && num_outputs <= 1) {
-    tile_n = p.tile_n;
   } else {
+    const bool forced = p.tile_n > 0 && num_outputs <= 1;
     double best = 1e300;
     for (int cand = 256; cand >= 192; cand -= 32) {
+      if (forced && cand != p.tile_n) continue;
       if (cand % 64 != 0 && num_outputs > 1) continue;
       const long long tiles = static_cast<long long>(p.tiles_m) * ((p.n + cand - 1) / cand);
-      const long long waves = (tiles + workers - 1) / workers;
-      const double cost = static_cast<double>(waves) * (cand + 9) * (cand == 224 ? 1.03 : 1.0);
-      if (cost < best * 0.999) { best = cost; tile_n = cand; }
+      const long long full = tiles / workers, rest = tiles % workers;
+      for (int s = 1; s <= 4; s *= 2) {
+        const int width = cand / s;
+        if (s > 1 && (rest == 0 || rest * s > workers || width % 32 != 0 || (num_outputs > 1 && width % 64 != 0))) continue;
+        const double tail = rest == 0 ? 0.0 : s == 1 ? 1.0 : kMode == kModeGrouped ? 0.8 : s == 2 ? 0.6 : 0.5;
+        const double cost = (static_cast<double>(full) + tail) * (cand + 9) * (cand == 224 ? 1.03 : 1.0);
+        if (cost < best * 0.999) { best = cost; tile_n = cand; split = s; }
+      }
     }
   }
   p.tile_n = tile_n;
   p.tiles_n = (p.n + tile_n - 1) / tile_n;
+  {
+    const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    p.split = split;
+    p.full_tiles = split > 1 ? static_cast<int>(tiles - tiles % workers) : static_cast<int>(tiles);
+    p.total_items = p.full_tiles + static_cast<int>(tiles - p.full_tiles) * split;
+  }
   const int w_box_rows = kMode == kModeBiased ? Cfg::kBRowsLoad : tile_n / kCtas;
   p.stage_tx = Cfg::kABytes + w_box_rows * Cfg::kBlockK;
   // rows of A per raster group: about 32 MiB of activations, so they stay in L2
@@ -157,10 +173,14 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   p.group_m = static_cast<int>(group_rows / (Cfg::kBlockM * kCtas));
   if (p.group_m < 1) p.group_m = 1;
   if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
-  CUtensorMap map_a, map_w;
+  CUtensorMap map_a, map_w, map_w_slice;
   err = make_map(&map_a, a, static_cast<uint64_t>(p.m) * p.groups, p.k, Cfg::kBlockM);
   if (err != cudaSuccess) return err;
   err = make_map(&map_w, w, p.n, static_cast<uint64_t>(p.k) * p.groups, w_box_rows);
+  if (err != cudaSuccess) return err;
+  const int slice_box_rows = p.split > 1 ? tile_n / p.split / kCtas : w_box_rows;
+  p.stage_tx_slice = Cfg::kABytes + slice_box_rows * Cfg::kBlockK;
+  err = make_map(&map_w_slice, w, p.n, static_cast<uint64_t>(p.k) * p.groups, slice_box_rows);
   if (err != cudaSuccess) return err;
   OutputMaps out_maps = {};
   void* local_only[1] = {p.out};
@@ -181,7 +201,7 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
     return cudaErrorInvalidValue;   // several destinations need the tile-store path
   }
 
-  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const long long tiles = p.total_items;
   cudaLaunchConfig_t config = {};
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -202,7 +222,7 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   config.blockDim = dim3(Cfg::kThreads);
   config.dynamicSmemBytes = Cfg::kSmemBytes;
   config.stream = stream;
-  return cudaLaunchKernelEx(&config, kernel, map_a, map_w, out_maps, p);
+  return cudaLaunchKernelEx(&config, kernel, map_a, map_w, map_w_slice, out_maps, p);
 }
 
 // Launch with programmatic stream serialization: the kernel may become resident while the kernel

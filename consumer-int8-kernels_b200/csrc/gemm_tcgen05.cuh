@@ -52,6 +52,10 @@ struct GemmParams {
   int tile_n;                 // output channels per tile: 256, or narrower (a multiple of 32) when that
                               // packs the tiles into fewer, fuller waves; 240 for the biased form
   int stage_tx;               // bytes one CTA's TMA loads deliver per stage (A box + W box)
+  int stage_tx_slice;         // the same for a column slice (A box + the narrower W box)
+  int full_tiles;             // work items [0, full_tiles) are whole tiles (the complete waves)
+  int split;                  // each tile of the last, partial wave is cut into `split` column slices
+  int total_items;            // full_tiles + (tiles - full_tiles) * split
 };
 
 // Tensor maps of the output destinations: BF16 [M,N] matrices, boxes of 64 columns x 32 rows.
@@ -87,7 +91,23 @@ struct GemmConfig {
 // Tile order: row tiles are walked in groups of group_m; inside a group the row tile index runs
 // fastest, then the channel tile. One wave of CTAs then touches a bounded set of A rows (which
 // stay in L2 while the weights stream past) instead of every row of a tall A.
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mt, int& nt) {
+//
+// Work items: the tiles of the complete waves are whole; the tiles of the last, partial wave are cut
+// into `split` column slices of tile_n/split accumulator columns that spread over the CTAs the wave
+// would leave idle. A slice still streams the full K extent of A, but its MMAs are narrower and take
+// about N/2 cycles each, so a half slice lasts ~0.6 of a whole tile.
+// item -> tile (mt, nt), first column n_off and width n_width inside the tile.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int item, int& mt, int& nt, int& n_off,
+                                            int& n_width) {
+  int tile = item;
+  n_off = 0;
+  n_width = p.tile_n;
+  if (item >= p.full_tiles) {
+    const int extra = item - p.full_tiles;
+    tile = p.full_tiles + extra / p.split;
+    n_width = p.tile_n / p.split;
+    n_off = (extra % p.split) * n_width;
+  }
   const int per_group = p.group_m * p.tiles_n;
   const int group = tile / per_group;
   const int within = tile - group * per_group;
@@ -106,6 +126,7 @@ template <int kCtas, int kMode>
 __global__ void __launch_bounds__(GemmConfig<kCtas, kMode>::kThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ CUtensorMap map_w_slice,
                const __grid_constant__ OutputMaps out_maps, const GemmParams p) {
   using Cfg = GemmConfig<kCtas, kMode>;
   extern __shared__ uint8_t smem_raw[];
@@ -144,6 +165,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_w);
+    if (p.split > 1) prefetch_tensormap(&map_w_slice);
     for (int d = 0; d < p.num_outputs; ++d) prefetch_tensormap(&out_maps.map[d]);
   }
   if constexpr (kMode == kModeBiased) {
@@ -175,9 +197,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   pdl_wait();
 
   const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;   // per group
-  const int total_tiles = p.tiles_m * p.tiles_n;
-  // accumulator columns the MMA produces per tile (the biased form adds its 16 ones columns)
-  const int mma_n = kMode == kModeBiased ? Cfg::kTileN : p.tile_n;
+  const int total_tiles = p.total_items;   // work items: whole tiles, then column slices
   const int first_tile = kCtas == 2 ? (blockIdx.x >> 1) : blockIdx.x;
   const int tile_stride = kCtas == 2 ? (gridDim.x >> 1) : gridDim.x;
 
@@ -193,25 +213,29 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     const uint32_t leader_full0 = kCtas == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
     bool ok = true;
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-      int mt, nt;
-      tile_coords(p, tile, mt, nt);
+      int mt, nt, n_off, n_width;
+      tile_coords(p, tile, mt, nt, n_off, n_width);
       const int a_row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM;
-      const int w_row = nt * p.tile_n + rank * (p.tile_n / kCtas);   // a pair's CTAs supply half the rows each
+      // a pair's CTAs supply half the weight rows each; slices load through their own, narrower box
+      const int w_row = nt * p.tile_n + n_off + rank * (n_width / kCtas);
+      const bool slice = tile >= p.full_tiles;
+      const CUtensorMap* w_map = slice ? &map_w_slice : &map_w;
+      const uint32_t tx = static_cast<uint32_t>(slice ? p.stage_tx_slice : p.stage_tx) * kCtas;
       for (int g = 0; ok && g < p.groups; ++g) {
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) { ok = false; break; }
           if (elect_one()) {
-            if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), p.stage_tx * kCtas);
+            if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), tx);
             const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
             const uint32_t b_dst = a_dst + Cfg::kABytes;
             const uint32_t bar = leader_full0 + 8u * stage;
             const int kx = kb * Cfg::kBlockK;
             if constexpr (kCtas == 2) {
               tma_load_2d_pair(a_dst, &map_a, kx, g * p.m + a_row, bar);
-              tma_load_2d_pair(b_dst, &map_w, g * p.k + kx, w_row, bar);
+              tma_load_2d_pair(b_dst, w_map, g * p.k + kx, w_row, bar);
             } else {
               tma_load_2d(a_dst, &map_a, kx, g * p.m + a_row, bar);
-              tma_load_2d(b_dst, &map_w, g * p.k + kx, w_row, bar);
+              tma_load_2d(b_dst, w_map, g * p.k + kx, w_row, bar);
             }
           }
           __syncwarp();
@@ -227,8 +251,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       int stage = 0;
       uint32_t phase = 0, acc_iter = 0;
       bool ok = true;
-      const uint32_t idesc = idesc_i8(Cfg::kBlockM * kCtas, mma_n, /*b_unsigned=*/kMode == kModeBiased);
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
+        int mt, nt, n_off, n_width;
+        tile_coords(p, tile, mt, nt, n_off, n_width);
+        // accumulator columns the MMA produces (the biased form adds its 16 ones columns)
+        const uint32_t idesc = idesc_i8(Cfg::kBlockM * kCtas, kMode == kModeBiased ? Cfg::kTileN : n_width,
+                                        /*b_unsigned=*/kMode == kModeBiased);
         for (int g = 0; ok && g < p.groups; ++g, ++acc_iter) {
           const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
           if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag))) { ok = false; break; }
@@ -282,11 +310,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     bool ok = true;
     float total[kMode == kModeGrouped ? Cfg::kColsPerEpiWarp : 1];
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-      int mt, nt;
-      tile_coords(p, tile, mt, nt);
+      int mt, nt, n_off, n_width;
+      tile_coords(p, tile, mt, nt, n_off, n_width);
       const int row0 = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM + quarter * 32;
       const int row = row0 + lane;
-      const int n0 = nt * p.tile_n;                       // first output column of this tile
+      const int n0 = nt * p.tile_n + n_off;               // first output column of this item
       for (int g = 0; g < p.groups; ++g, ++acc_iter) {
         const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
         if (!mbar_wait<kCtas == 2>(tmem_full_bar(buf), acc_phase, abort_flag)) { ok = false; break; }
@@ -306,12 +334,12 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int chunk = 0; chunk < kChunks; ++chunk) {
           const int tile_col = col_base + chunk * 64;     // first accumulator column of this 64-wide box
-          if (tile_col >= mma_n) continue;                // a narrow tile has fewer boxes
+          if (tile_col >= n_width) continue;              // a narrow tile or a slice has fewer boxes
           const int c0 = n0 + tile_col;                   // its first output column
           const bool store_box = (kMode != kModeGrouped || last_group) && c0 < p.n;
-          // a box that straddles the tile's right edge (tile_n is a multiple of 32, not of 64) must not
+          // a box that straddles the item's right edge (its width is a multiple of 32, not of 64) must not
           // be written as a whole 64-wide TMA box: its valid half goes out with direct stores
-          const bool tma_box = tma_out && tile_col + 64 <= p.tile_n;
+          const bool tma_box = tma_out && tile_col + 64 <= n_width;
           uint8_t* box = my_staging + (store_iter % Cfg::kStoreBufs) * Cfg::kStoreBoxBytes;
           if (tma_box && store_box && store_iter >= Cfg::kStoreBufs) {
             // the box is reused only after its previous stores have finished reading it
@@ -332,11 +360,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
                 total[t] = g == 0 ? term : __fadd_rn(total[t], term);
               }
             }
-            if (!store_box || h0 >= p.n || tile_col + half * 32 >= p.tile_n) continue;
+            if (!store_box || h0 >= p.n || tile_col + half * 32 >= n_width) continue;
             // channel scales of these 32 columns: lane j holds sw[h0 + j]
             const float my_sw = (h0 + lane < p.n) ? __bfloat162float(p.sw[h0 + lane]) : 0.f;
             const int limit = kMode == kModeBiased
-                                  ? min(p.n - h0, p.tile_n - (tile_col + half * 32))
+                                  ? min(p.n - h0, n_width - (tile_col + half * 32))
                                   : p.n - h0;
             if constexpr (kMode == kModeBiased) {
 #pragma unroll
