@@ -375,14 +375,23 @@ cudaError_t launch_quantize(const void* x, int8_t* q, float* s, int rows, int k,
     else if (per_lane <= 2) CI8_WARP(2);
     else CI8_WARP(4);
 #undef CI8_WARP
+  } else if (vector_ok && packs <= 128 * 8) {
+    // rows up to K = 8192: 128 threads per row, two rows per CTA, no idle pack slots at K = 4096 / 5120
+    const int per_thread = (packs + 127) / 128;
+#define CI8_HALF(P) launch_quantize_vec<128, P>(x, q, s, rows, k, m, groups, stream)
+    if (per_thread <= 1) CI8_HALF(1);
+    else if (per_thread <= 2) CI8_HALF(2);
+    else if (per_thread <= 3) CI8_HALF(3);
+    else if (per_thread <= 4) CI8_HALF(4);
+    else if (per_thread <= 5) CI8_HALF(5);
+    else if (per_thread <= 6) CI8_HALF(6);
+    else CI8_HALF(8);
+#undef CI8_HALF
   } else if (vector_ok && packs <= 256 * 32) {
     // one 256-thread CTA per row
     const int per_thread = (packs + 255) / 256;
 #define CI8_CTA(P) launch_quantize_vec<256, P>(x, q, s, rows, k, m, groups, stream)
-    if (per_thread <= 1) CI8_CTA(1);
-    else if (per_thread <= 2) CI8_CTA(2);
-    else if (per_thread <= 3) CI8_CTA(3);
-    else if (per_thread <= 4) CI8_CTA(4);
+    if (per_thread <= 5) CI8_CTA(5);
     else if (per_thread <= 6) CI8_CTA(6);
     else if (per_thread <= 9) CI8_CTA(9);
     else if (per_thread <= 12) CI8_CTA(12);

@@ -28,43 +28,53 @@ __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w 
 __device__ __forceinline__ int quantize_one(float v, float scale) {
   return max(-127, min(127, __float2int_rn(__fdiv_rn(v, scale))));
 }
-__device__ __forceinline__ uint32_t quantize_four_exact(uint32_t w0, uint32_t w1, float scale) {
-  const int q0 = quantize_one(bf16_lo(w0), scale), q1 = quantize_one(bf16_hi(w0), scale);
-  const int q2 = quantize_one(bf16_lo(w1), scale), q3 = quantize_one(bf16_hi(w1), scale);
-  return (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | (static_cast<uint32_t>(q3) << 24);
-}
-
 constexpr float kRoundMagic = 12582912.f;   // 1.5 * 2^23
 constexpr float kTieGuard = 0.49995f;       // |q' - rint(q')| below this: no tie within the error bound
 
-// Short path for one value: returns the FADD result whose low byte is the code and clears `safe`
-// when the value is not provably away from a rounding tie (NaN compares false, so NaN and
-// inf * 0 land on the exact path too).
+// Short path for one value: returns the FMA result whose low byte is the code and clears `safe`
+// when the value is not provably away from a rounding tie. shifted = RN(v * inverse + 1.5 * 2^23) is
+// the exact product rounded to the nearest integer (ties to even); the second FMA gives the exact
+// product's distance from that integer. |v * inverse - v / scale| <= 127.5 * 2^-24 and the reference's
+// own rounding of v / scale moves it by as much again, so outside the guard band both round alike.
+// NaN compares false, so NaN and inf * 0 land on the exact path too.
 __device__ __forceinline__ uint32_t quantize_fast(float v, float inverse, bool& safe) {
-  const float q = __fmul_rn(v, inverse);
-  const float shifted = __fadd_rn(q, kRoundMagic);
+  const float shifted = __fmaf_rn(v, inverse, kRoundMagic);
   const float rounded = __fsub_rn(shifted, kRoundMagic);
-  safe = safe && (fabsf(__fsub_rn(q, rounded)) < kTieGuard);
+  const float residual = __fmaf_rn(v, inverse, -rounded);
+  safe = safe && (fabsf(residual) < kTieGuard);
   return __float_as_uint(shifted);
 }
 
-// Eight BF16 values (one 16-byte pack) -> eight codes (8 bytes).
+// Running maximum of |x| over packed BF16 pairs: one LOP3 and one packed max per two values. The
+// packed max returns the other operand when one is NaN, which is what fmaxf does.
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t running, uint32_t pair) {
+  uint32_t result;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(result) : "r"(running), "r"(pair & 0x7fff7fffu));
+  return result;
+}
+
+// Eight BF16 values (one 16-byte pack) -> eight codes (8 bytes). BF16 inputs hit exact rounding ties
+// far more often than random reals would (x * 127 / absmax is a ratio of small integers): about one
+// warp-pack in eight holds one, so the repair redoes only the offending values, each with the
+// reference's division, instead of the whole pack.
 __device__ __forceinline__ uint2 quantize_pack(const uint4& pack, float scale, float inverse) {
+  const float v[8] = {bf16_lo(pack.x), bf16_hi(pack.x), bf16_lo(pack.y), bf16_hi(pack.y),
+                      bf16_lo(pack.z), bf16_hi(pack.z), bf16_lo(pack.w), bf16_hi(pack.w)};
+  uint32_t t[8];
   bool safe = true;
-  const uint32_t t0 = quantize_fast(bf16_lo(pack.x), inverse, safe);
-  const uint32_t t1 = quantize_fast(bf16_hi(pack.x), inverse, safe);
-  const uint32_t t2 = quantize_fast(bf16_lo(pack.y), inverse, safe);
-  const uint32_t t3 = quantize_fast(bf16_hi(pack.y), inverse, safe);
-  const uint32_t t4 = quantize_fast(bf16_lo(pack.z), inverse, safe);
-  const uint32_t t5 = quantize_fast(bf16_hi(pack.z), inverse, safe);
-  const uint32_t t6 = quantize_fast(bf16_lo(pack.w), inverse, safe);
-  const uint32_t t7 = quantize_fast(bf16_hi(pack.w), inverse, safe);
-  if (safe) {
-    const uint32_t lo = __byte_perm(__byte_perm(t0, t1, 0x0040), __byte_perm(t2, t3, 0x0040), 0x5410);
-    const uint32_t hi = __byte_perm(__byte_perm(t4, t5, 0x0040), __byte_perm(t6, t7, 0x0040), 0x5410);
-    return make_uint2(lo, hi);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) t[j] = quantize_fast(v[j], inverse, safe);
+  if (!safe) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      bool mine = true;
+      quantize_fast(v[j], inverse, mine);
+      if (!mine) t[j] = static_cast<uint32_t>(quantize_one(v[j], scale));
+    }
   }
-  return make_uint2(quantize_four_exact(pack.x, pack.y, scale), quantize_four_exact(pack.z, pack.w, scale));
+  const uint32_t lo = __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410);
+  const uint32_t hi = __byte_perm(__byte_perm(t[4], t[5], 0x0040), __byte_perm(t[6], t[7], 0x0040), 0x5410);
+  return make_uint2(lo, hi);
 }
 
 // Rows are walked in INPUT order so that consecutive teams read consecutive memory. Input row i:
@@ -110,7 +120,7 @@ __device__ __forceinline__ void load_row(uint4 (&pack)[kPacks], const uint16_t* 
   }
 }
 
-// kTeam threads per row (32, 256 or 512), kPacks 16-byte packs per thread; 256 threads per CTA
+// kTeam threads per row (32, 128, 256 or 512), kPacks 16-byte packs per thread; 256 threads per CTA
 // (512 when the team is that wide). Rows of up to 3 packs per thread run one team per row with many small CTAs resident (measured
 // faster there); wider rows (4..9 packs) use a persistent grid in which a team strides over the
 // rows and loads its next row before it reduces and converts the current one, so loads stay in
@@ -142,26 +152,26 @@ quantize_rows_vec_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
   for (int64_t base = static_cast<int64_t>(blockIdx.x) * kRowsPerCta, iter = 0; base < rows;
        base += stride, row += stride, ++iter) {
     if constexpr (kPrefetch) load_row<kTeam, kPacks, kSwiGLU>(next, x, row + stride, rows, k, member);
-    float maximum = 0.f;
+    uint32_t packed_max = 0u;
 #pragma unroll
     for (int i = 0; i < kPacks; ++i) {
-      const uint32_t w[4] = {pack[i].x, pack[i].y, pack[i].z, pack[i].w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        maximum = fmaxf(maximum, fabsf(bf16_lo(w[j])));
-        maximum = fmaxf(maximum, fabsf(bf16_hi(w[j])));
-      }
+      packed_max = absmax_bf16x2(packed_max, pack[i].x);
+      packed_max = absmax_bf16x2(packed_max, pack[i].y);
+      packed_max = absmax_bf16x2(packed_max, pack[i].z);
+      packed_max = absmax_bf16x2(packed_max, pack[i].w);
     }
+    float maximum = fmaxf(bf16_lo(packed_max), bf16_hi(packed_max));
 #pragma unroll
     for (int mask = 16; mask; mask >>= 1)
       maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, mask));
-    if constexpr (kTeam >= 256) {
-      float* slot = maxima[iter & 1];      // alternating slots: one barrier per row is enough
-      if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = maximum;
+    if constexpr (kTeam > 32) {
+      constexpr int kWarpsPerTeam = kTeam / 32;
+      float* slot = maxima[iter & 1] + (threadIdx.x / kTeam) * kWarpsPerTeam;   // alternating slots: one barrier per row
+      if ((threadIdx.x & 31) == 0) slot[(threadIdx.x % kTeam) >> 5] = maximum;
       __syncthreads();
       maximum = slot[0];
 #pragma unroll
-      for (int i = 1; i < kWarps; ++i) maximum = fmaxf(maximum, slot[i]);
+      for (int i = 1; i < kWarpsPerTeam; ++i) maximum = fmaxf(maximum, slot[i]);
     }
     const float scale = fmaxf(__fdiv_rn(maximum, 127.f), 1e-20f);
     const float inverse = __fdiv_rn(1.f, scale);
