@@ -13,6 +13,7 @@
 #include "decode_splitk.cuh"
 #include "gemm_tcgen05.cuh"
 #include "gemv_w8a16.cuh"
+#include "q8_block.cuh"
 #include "quantize.cuh"
 
 namespace {
@@ -455,6 +456,31 @@ __global__ void wait_timeout_selftest_kernel(unsigned long long deadline_ns, int
 
 }  // namespace
 
+// ------------------------------------------------------------------ block-32 (Q8_0) launch
+cudaError_t launch_q8_block(const void* x, int8_t* a, float* sa, const int8_t* w, const void* sw, void* y, int m,
+                            int n, int k, cudaStream_t stream) {
+  using Cfg = Q8BlockConfig;
+  static std::atomic<uint64_t> smem_done{0};
+  cudaError_t err = ensure_smem(q8_block_mm_kernel, Cfg::kSmemBytes, smem_done);
+  if (err != cudaSuccess) return err;
+  const long long blocks = static_cast<long long>(m) * (k / 32);
+  err = launch_serialized(q8_block_quantize_kernel, static_cast<unsigned>((blocks + 255) / 256), 256, 0, stream,
+                          static_cast<const uint16_t*>(x), a, sa, static_cast<int64_t>(blocks));
+  if (err != cudaSuccess) return err;
+  Q8BlockParams p{sa, static_cast<const __half*>(sw), static_cast<__nv_bfloat16*>(y), m, n, k, 0, 0};
+  p.tiles_m = (m + Cfg::kBlockM - 1) / Cfg::kBlockM;
+  p.tiles_n = (n + Cfg::kTileN - 1) / Cfg::kTileN;
+  CUtensorMap map_a, map_w;
+  err = make_map(&map_a, a, m, k, Cfg::kBlockM);
+  if (err != cudaSuccess) return err;
+  err = make_map(&map_w, w, n, k, Cfg::kTileN);
+  if (err != cudaSuccess) return err;
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const int sms = sm_count();
+  return launch_serialized(q8_block_mm_kernel, static_cast<unsigned>(tiles < sms ? tiles : sms), Cfg::kThreads,
+                           Cfg::kSmemBytes, stream, map_a, map_w, p);
+}
+
 // ====================================================================== C ABI
 extern "C" {
 
@@ -662,6 +688,16 @@ int ci8_selftest_wait_timeout(unsigned deadline_us, int* gave_up, ci8_stream_t s
 
 // Test hook: the decode kernel with a forced split-K factor (1, 2 or 4); weights_biased != 0
 // selects the UINT8 form. Same contract as ci8_fused_channel_mm / ci8_channel_mm with m <= 16.
+int ci8_q8_block_mm(const void* x, int8_t* a, float* sa, const int8_t* w, const void* sw, void* y, int m, int n,
+                    int k, ci8_stream_t stream) {
+  if (!x || !a || !sa || !w || !sw || !y || m <= 0 || n <= 0 || k <= 0 || k % 32 != 0 || k > 65536 ||
+      static_cast<long long>(m) * k > INT32_MAX || static_cast<long long>(n) * k > INT32_MAX ||
+      static_cast<long long>(m) * n > INT32_MAX || !aligned(x, 16) || !aligned(a, 16) || !aligned(w, 16) ||
+      !aligned(sw, 2) || !aligned(sa, 4))
+    return kInvalid;
+  return launch_q8_block(x, a, sa, w, sw, y, m, n, k, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int ci8_decode_mm_split(const int8_t* a, const void* w, const float* a_scale, const void* w_scale,
                         int32_t* workspace, void* out, int m, int n, int k, int split, int weights_biased,
                         ci8_stream_t stream) {

@@ -92,6 +92,16 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
                            const void* w_scale, void* out, int m, int n, int groups,
                            ci8_stream_t stream);
 
+/* Replaces q8_block_int8 (reference benchmarks/cuda/q8_block_int8.cu:150-160, a raw C entry point
+ * bound with ctypes by benchmarks/benchmark_q8_block_int8.py:36-39; same argument order). Block-32
+ * (GGUF Q8_0) W8A8: x BF16 [m,k] is quantized per 32 values into a INT8 [m,k] with sa FP32
+ * [m,k/32] (both caller-owned scratch that is also an output), then
+ * y[m,n] = bf16(sum over blocks b ascending of fma(float(dot_b), sa[m,b] * float(sw[n,b]), .)),
+ * dot_b the INT32 product of the block's 32 codes; w INT8 [n,k] (codes in [-128,127]), sw FP16
+ * [n,k/32], y BF16 [m,n]. k % 32 == 0, k <= 65536; x, a and w 16-byte aligned. */
+int ci8_q8_block_mm(const void* x, int8_t* a, float* sa, const int8_t* w, const void* sw, void* y,
+                    int m, int n, int k, ci8_stream_t stream);
+
 /* fused_channel_mm for an output-channel shard, with the all-gather of the result fused into the
  * GEMM's epilogue. The reference has no collective (its serving stack gathers column-parallel
  * results outside the library, benchmarks/microbench.py:187); this entry point replaces

@@ -12,6 +12,7 @@
  * Reference anchors (paths inside the reference project):
  *   quantizer  csrc/kernels.cu:13-35        product   csrc/kernels.cu:95-114, tests/test_cuda_ops.py:488,596
  *   epilogue   csrc/kernels.cu:120          grouped   csrc/kernels.cu:47-48
+ *   block-32   benchmarks/cuda/q8_block_int8.cu:11-69 (quantizer and per-block rescaled product)
  */
 #include <math.h>
 #include <stdint.h>
@@ -96,5 +97,63 @@ void ci8o_grouped_epilogue(const int32_t* acc, const float* sa, const uint16_t* 
         total = g ? total + term : term;
       }
       out[(int64_t)r * n + c] = f32_to_bf16(total * bf16_to_f32(sw[c]));
+    }
+}
+
+/* IEEE binary16 -> binary32 (exact). */
+static float f16_to_f32(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  uint32_t exponent = (h >> 10) & 0x1fu, mantissa = h & 0x3ffu, bits;
+  if (exponent == 0) {
+    if (mantissa == 0) {
+      bits = sign;
+    } else {
+      int shift = 0;
+      while (!(mantissa & 0x400u)) { mantissa <<= 1; ++shift; }
+      mantissa &= 0x3ffu;
+      bits = sign | ((uint32_t)(113 - shift) << 23) | (mantissa << 13);
+    }
+  } else if (exponent == 31) {
+    bits = sign | 0x7f800000u | (mantissa << 13);
+  } else {
+    bits = sign | ((exponent + 112) << 23) | (mantissa << 13);
+  }
+  float f;
+  memcpy(&f, &bits, 4);
+  return f;
+}
+
+/* benchmarks/cuda/q8_block_int8.cu:11-24 — one scale per 32 values, scale = max(absmax/127, 1e-20),
+ * code = int8(round_half_even(v / scale)); NaN quotients give 0 as __float2int_rn does. */
+void ci8o_q8_block_quantize(const uint16_t* x, int8_t* q, float* scales, int64_t blocks) {
+  for (int64_t b = 0; b < blocks; ++b) {
+    float maximum = 0.f;
+    for (int i = 0; i < 32; ++i) maximum = fmaxf(maximum, fabsf(bf16_to_f32(x[b * 32 + i])));
+    const float scale = fmaxf(maximum / 127.f, 1e-20f);
+    for (int i = 0; i < 32; ++i) {
+      const float quotient = bf16_to_f32(x[b * 32 + i]) / scale;
+      q[b * 32 + i] = isnan(quotient) ? 0 : (int8_t)rintf(quotient);
+    }
+    scales[b] = scale;
+  }
+}
+
+/* benchmarks/cuda/q8_block_int8.cu:26-69 — per 32-wide block an INT32 dot product, then
+ * sum = fma(float(dot), sa * sw, sum) in ascending block order (the contracted form of the
+ * reference's `sum += float(acc) * (sa * sw)`), rounded to BF16 at the end. sw is FP16. */
+void ci8o_q8_block_mm(const int8_t* a, const int8_t* w, const float* sa, const uint16_t* sw, uint16_t* y, int m,
+                      int n, int k) {
+  const int blocks = k / 32;
+  for (int r = 0; r < m; ++r)
+    for (int c = 0; c < n; ++c) {
+      float sum = 0.f;
+      for (int b = 0; b < blocks; ++b) {
+        int32_t dot = 0;
+        for (int i = 0; i < 32; ++i)
+          dot += (int32_t)a[(int64_t)r * k + b * 32 + i] * (int32_t)w[(int64_t)c * k + b * 32 + i];
+        const float scale = sa[(int64_t)r * blocks + b] * f16_to_f32(sw[(int64_t)c * blocks + b]);
+        sum = fmaf((float)dot, scale, sum);
+      }
+      y[(int64_t)r * n + c] = f32_to_bf16(sum);
     }
 }

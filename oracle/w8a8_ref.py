@@ -247,3 +247,45 @@ def pack_allspark_ref(codes_u8: torch.Tensor, scales: torch.Tensor):
     packed_scales = torch.zeros(padded, dtype=scales.dtype)
     packed_scales[torch.from_numpy(scale_index)] = scales
     return torch.from_numpy(flat).view(padded, k), packed_scales
+
+
+def q8_block_quantize_ref(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """BF16 [M,K] -> (INT8 codes [M,K], FP32 scales [M,K/32]): the row quantizer applied to every
+    32 consecutive values (benchmarks/cuda/q8_block_int8.cu:11-24; its oracle in
+    benchmarks/benchmark_q8_block_int8.py:90-93 is the same absmax/127 formula)."""
+    m, k = x.shape
+    codes, scales = quantize_rows_ref(x.reshape(m * (k // 32), 32))
+    return codes.reshape(m, k), scales.reshape(m, k // 32)
+
+
+def q8_block_mm_ref(a: torch.Tensor, w: torch.Tensor, sa: torch.Tensor, sw: torch.Tensor) -> torch.Tensor:
+    """Block-32 W8A8 product: a INT8 [M,K], w INT8 [N,K], sa FP32 [M,K/32], sw FP16 [N,K/32] -> BF16
+    [M,N] with sum = fma(float(dot_b), sa_b * sw_b, sum) over ascending blocks
+    (benchmarks/cuda/q8_block_int8.cu:44-62 with the multiply-add contracted). The FMA is emulated
+    in FP64: the product of an integer below 2^20 and an FP32 scale is exact there, so only the
+    final rounding of the sum to FP32 is done twice (FP64, then FP32)."""
+    m, k = a.shape
+    n = w.shape[0]
+    blocks = k // 32
+    total = torch.zeros(m, n, dtype=torch.float32)
+    a64 = a.reshape(m, blocks, 32).double()
+    w64 = w.reshape(n, blocks, 32).double()
+    for b in range(blocks):
+        dot = a64[:, b] @ w64[:, b].T                                   # exact: |dot| < 2^20
+        scale = sa[:, b, None].float() * sw[None, :, b].float()        # one FP32 rounding, as on the GPU
+        total = (dot * scale.double() + total.double()).float()
+    return total.bfloat16()
+
+
+def q8_block_mm_loose_ref(a, w, sa, sw) -> torch.Tensor:
+    """The formula of the reference's own acceptance test, literally
+    (benchmarks/benchmark_q8_block_int8.py:104-109): FP32 multiply and add, no FMA; the test
+    there allows rtol 0.008 against it."""
+    m, k = a.shape
+    n = w.shape[0]
+    blocks = k // 32
+    total = torch.zeros(m, n)
+    for b in range(blocks):
+        dot = a.reshape(m, blocks, 32)[:, b].float() @ w.reshape(n, blocks, 32)[:, b].float().T
+        total += dot * (sa[:, b, None] * sw[None, :, b].float())
+    return total.bfloat16()

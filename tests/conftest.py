@@ -42,6 +42,5 @@ def ops():
 def c_oracle():
     """The scalar C checker (oracle/ci8_oracle.c), built on demand."""
     target = ROOT / "oracle" / "libci8_oracle.so"
-    if not target.exists():
-        subprocess.run(["make", "-C", str(ROOT / "oracle")], check=True)
+    subprocess.run(["make", "-s", "-C", str(ROOT / "oracle")], check=True)   # rebuilds only when the source is newer
     return ctypes.CDLL(str(target))

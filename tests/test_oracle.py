@@ -186,3 +186,36 @@ def test_allspark_unpack_restatement_follows_the_reference_index_arithmetic():
     repacked, repacked_scales = ref.pack_allspark_ref((codes.short() + 128).to(torch.uint8), scales)
     again, again_scales = ref.unpack_allspark_ref(repacked, repacked_scales, n, k)
     assert torch.equal(again, codes) and torch.equal(again_scales.view(torch.int16), scales.view(torch.int16))
+
+
+def _q8_case(m, n, k, seed):
+    """Inputs shaped like the reference's benchmark (benchmarks/benchmark_q8_block_int8.py:57-66): Q8_0
+    codes over the whole INT8 range, FP16 block scales ~0.01, activations ~0.1 with one all-zero
+    block and one block a hundred times larger."""
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randint(-128, 128, (n, k), dtype=torch.int8, generator=g)
+    sw = (torch.randn(n, k // 32, generator=g) * 0.01).half()
+    x = (torch.randn(m, k, generator=g) * 0.1).bfloat16()
+    x[:, :32] = 0
+    if k >= 64:
+        x[:, 32:64] *= 100
+    return x, w, sw
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 32), (17, 33, 96), (129, 65, 256), (8, 40, 1024)])
+def test_block32_checkers_agree_and_sit_inside_the_reference_tolerance(c_oracle, m, n, k):
+    x, w, sw = _q8_case(m, n, k, 100 + m)
+    codes, sa = ref.q8_block_quantize_ref(x)
+    c_codes, c_sa = torch.empty_like(codes), torch.empty_like(sa)
+    c_oracle.ci8o_q8_block_quantize(ptr(x), ptr(c_codes), ptr(c_sa), ctypes.c_int64(m * (k // 32)))
+    assert torch.equal(codes, c_codes) and torch.equal(sa, c_sa)
+    # the reference's own assertions on the quantizer (benchmark_q8_block_int8.py:90-101)
+    blocks = x.float().reshape(m, k // 32, 32)
+    expected_scale = (blocks.abs().amax(-1) / 127).clamp_min(1e-20)
+    torch.testing.assert_close(sa, expected_scale, rtol=1e-6, atol=0)
+    assert ((codes.reshape(m, k // 32, 32).float() - blocks / expected_scale[..., None]).abs() <= 0.50002).all()
+    y = ref.q8_block_mm_ref(codes, w, sa, sw)
+    c_y = torch.empty_like(y)
+    c_oracle.ci8o_q8_block_mm(ptr(codes), ptr(w), ptr(sa), ptr(sw), ptr(c_y), m, n, k)
+    assert torch.equal(y.view(torch.int16), c_y.view(torch.int16))
+    torch.testing.assert_close(y, ref.q8_block_mm_loose_ref(codes, w, sa, sw), rtol=0.008, atol=1e-5)
