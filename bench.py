@@ -452,6 +452,26 @@ def other_configs(ops, workloads, device, peaks):
     tops = 2.0 * m * n * groups * 4096 / ms / 1e9
     results["grouped"] = dict(gemm_ms=ms, tops=tops, frac_tensor=tops / tensor_peak, frac_nominal_4500=tops / 4500,
                               quantize_us=ms_q * 1e3, quantize_gbs=(3 * m * groups * 4096 + 4 * m * groups) / ms_q / 1e6)
+    del xs, wd, codes, out
+    # block-32 (Q8_0) W8A8 through the C ABI, at the shapes of the reference's benchmark
+    # (benchmarks/benchmark_q8_block_int8.py:44: n=1024, k=4096); quantizer + product per call
+    import ctypes
+    n, k = 1024, 4096
+    w = torch.randint(-128, 128, (n, k), dtype=torch.int8, generator=gen).to(device)
+    sw = (torch.randn(n, k // 32, generator=gen) * 0.01).half().to(device)
+    for m in (16, 4096):
+        x = (torch.randn(m, k, generator=gen) * 0.1).bfloat16().to(device)
+        a = torch.empty(m, k, dtype=torch.int8, device=device)
+        sa = torch.empty(m, k // 32, device=device)
+        y = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+
+        def q8(_i, x=x, a=a, sa=sa, y=y, m=m):
+            stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            rc = ops.libci8.ci8_q8_block_mm(*(ctypes.c_void_p(t.data_ptr()) for t in (x, a, sa, w, sw, y)), m, n, k, stream)
+            assert rc == 0, rc
+
+        ms = _time_graph(q8, 10)
+        results[f"q8_block_m{m}"] = dict(us=ms * 1e3, tops=2.0 * m * n * k / ms / 1e9)
     return results
 
 

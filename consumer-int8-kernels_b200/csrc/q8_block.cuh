@@ -12,8 +12,10 @@
 // 128 x 64 accumulators fill one 256-column half of TMEM while the epilogue warps drain the other
 // half. The kernel is bound by the CUDA cores, not by the tensor pipe: every (row, channel, block)
 // costs an INT32->FP32 conversion, the scale product and the FMA (the four MMAs of a stage take
-// ~130 cycles, draining their accumulators ~1000), which is inherent to per-block FP32 rescaling
-// of INT32 partials — the block-scaled tcgen05 kinds take floating-point operands only.
+// ~200 cycles, draining their accumulators ~1700), which is inherent to per-block FP32 rescaling
+// of INT32 partials — the block-scaled tcgen05 kinds take floating-point operands only. (Replacing
+// the conversion instruction by an integer add and a packed FP32 subtract of 1.5 * 2^23 was
+// measured slower.)
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -195,38 +197,80 @@ q8_block_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       const int row = mt * Cfg::kBlockM + quarter * 32 + lane;
       const int col0 = nt * Cfg::kTileN + half * 32;          // first channel of this warp
       const int my_col = col0 + lane;                         // the channel whose scales this lane fetches
-      float sum[32];
+      float2 sum2[16];                                        // sums of channels 2i and 2i + 1
 #pragma unroll
-      for (int c = 0; c < 32; ++c) sum[c] = 0.f;
+      for (int c = 0; c < 16; ++c) sum2[c] = make_float2(0.f, 0.f);
+      // Scales of a stage's four blocks (zero past the end of K, of M or of N). Those of the next
+      // stage are fetched while the current one is processed, and kept as the raw loaded words: any
+      // arithmetic on them here would wait for the loads.
+      float4 next_row_scales;     // sa[row, 4 blocks]
+      uint2 next_channel_scales;  // sw[my_col, 4 blocks] as FP16 bit patterns
+      const bool vector_scales = blocks_in_row % Cfg::kBlocksPerStage == 0 &&
+                                 reinterpret_cast<uintptr_t>(p.sa) % 16 == 0 && reinterpret_cast<uintptr_t>(p.sw) % 8 == 0;
+      auto fetch_scales = [&](int kb) {
+        const int first = kb * Cfg::kBlocksPerStage;
+        next_row_scales = make_float4(0.f, 0.f, 0.f, 0.f);
+        next_channel_scales = make_uint2(0u, 0u);
+        if (first >= blocks_in_row) return;
+        const float* sa_row = p.sa + static_cast<size_t>(row) * blocks_in_row + first;
+        const uint16_t* sw_row = reinterpret_cast<const uint16_t*>(p.sw) + static_cast<size_t>(my_col) * blocks_in_row + first;
+        if (vector_scales) {
+          // the stage's four blocks are adjacent: one 16-byte and one 8-byte load per thread
+          if (row < p.m) next_row_scales = __ldg(reinterpret_cast<const float4*>(sa_row));
+          if (my_col < p.n) next_channel_scales = __ldg(reinterpret_cast<const uint2*>(sw_row));
+        } else {
+          const int live = min(Cfg::kBlocksPerStage, blocks_in_row - first);
+          if (row < p.m) {
+            next_row_scales.x = __ldg(sa_row);
+            if (live > 1) next_row_scales.y = __ldg(sa_row + 1);
+            if (live > 2) next_row_scales.z = __ldg(sa_row + 2);
+            if (live > 3) next_row_scales.w = __ldg(sa_row + 3);
+          }
+          if (my_col < p.n) {
+            uint32_t h0 = __ldg(sw_row), h1 = 0u, h2 = 0u, h3 = 0u;
+            if (live > 1) h1 = __ldg(sw_row + 1);
+            if (live > 2) h2 = __ldg(sw_row + 2);
+            if (live > 3) h3 = __ldg(sw_row + 3);
+            next_channel_scales = make_uint2(h0 | (h1 << 16), h2 | (h3 << 16));
+          }
+        }
+      };
+      fetch_scales(0);
       for (int kb = 0; kb < num_kb; ++kb, ++iter) {
         const uint32_t buf = iter & 1u, buf_phase = (iter >> 1) & 1u;
-        // scales of this stage's four blocks (zero past the end of K, of M or of N)
-        float row_scale[Cfg::kBlocksPerStage];
-#pragma unroll
-        for (int b = 0; b < Cfg::kBlocksPerStage; ++b) {
-          const int block = kb * Cfg::kBlocksPerStage + b;
-          const bool live = block < blocks_in_row;
-          row_scale[b] = (live && row < p.m) ? __ldg(p.sa + static_cast<size_t>(row) * blocks_in_row + block) : 0.f;
-          my_scales[b * 32 + lane] =
-              (live && my_col < p.n) ? __half2float(p.sw[static_cast<size_t>(my_col) * blocks_in_row + block]) : 0.f;
+        const float row_scale[Cfg::kBlocksPerStage] = {next_row_scales.x, next_row_scales.y, next_row_scales.z,
+                                                       next_row_scales.w};
+        {
+          const __half2 lo = *reinterpret_cast<const __half2*>(&next_channel_scales.x);
+          const __half2 hi = *reinterpret_cast<const __half2*>(&next_channel_scales.y);
+          my_scales[0 * 32 + lane] = __low2float(lo);
+          my_scales[1 * 32 + lane] = __high2float(lo);
+          my_scales[2 * 32 + lane] = __low2float(hi);
+          my_scales[3 * 32 + lane] = __high2float(hi);
         }
         __syncwarp();
+        fetch_scales(kb + 1);   // past the last stage every block index is out of range: zeros, no loads
         if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), buf_phase, abort_flag))) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * Cfg::kAccColumns + half * 32;
+        uint32_t v[2][32];
+        tmem_ld_32x32(taddr, v[0]);
 #pragma unroll
         for (int b = 0; b < Cfg::kBlocksPerStage; ++b) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + b * Cfg::kTileN, v);
-          tmem_ld_wait_for(v);
+          uint32_t (&cur)[32] = v[b & 1];
+          tmem_ld_wait_for(cur);
+          if (b + 1 < Cfg::kBlocksPerStage) tmem_ld_32x32(taddr + (b + 1) * Cfg::kTileN, v[(b + 1) & 1]);
           const float4* channel_scales = reinterpret_cast<const float4*>(my_scales + b * 32);   // broadcast reads
+          // packed FP32 arithmetic (two IEEE-rounded lanes per instruction): one multiply for two scale
+          // products, one FMA for two accumulations
+          const float2 rs2 = make_float2(row_scale[b], row_scale[b]);
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
             const float4 s = channel_scales[c >> 2];
-            sum[c] = __fmaf_rn(__int2float_rn(static_cast<int32_t>(v[c])), __fmul_rn(row_scale[b], s.x), sum[c]);
-            sum[c + 1] = __fmaf_rn(__int2float_rn(static_cast<int32_t>(v[c + 1])), __fmul_rn(row_scale[b], s.y), sum[c + 1]);
-            sum[c + 2] = __fmaf_rn(__int2float_rn(static_cast<int32_t>(v[c + 2])), __fmul_rn(row_scale[b], s.z), sum[c + 2]);
-            sum[c + 3] = __fmaf_rn(__int2float_rn(static_cast<int32_t>(v[c + 3])), __fmul_rn(row_scale[b], s.w), sum[c + 3]);
+            const float2 f01 = make_float2(__int2float_rn(static_cast<int32_t>(cur[c])), __int2float_rn(static_cast<int32_t>(cur[c + 1])));
+            const float2 f23 = make_float2(__int2float_rn(static_cast<int32_t>(cur[c + 2])), __int2float_rn(static_cast<int32_t>(cur[c + 3])));
+            sum2[c >> 1] = __ffma2_rn(f01, __fmul2_rn(rs2, make_float2(s.x, s.y)), sum2[c >> 1]);
+            sum2[(c >> 1) + 1] = __ffma2_rn(f23, __fmul2_rn(rs2, make_float2(s.z, s.w)), sum2[(c >> 1) + 1]);
           }
         }
         // this warp is done with the accumulator half and with its scale slots
@@ -240,14 +284,14 @@ q8_block_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int limit = p.n - col0;
         if (limit >= 32 && p.n % 8 == 0 && reinterpret_cast<uintptr_t>(p.y) % 16 == 0) {
 #pragma unroll
-          for (int c = 0; c < 32; c += 8)
-            *reinterpret_cast<uint4*>(dst + c) =
-                make_uint4(pack_bf16x2(sum[c], sum[c + 1]), pack_bf16x2(sum[c + 2], sum[c + 3]),
-                           pack_bf16x2(sum[c + 4], sum[c + 5]), pack_bf16x2(sum[c + 6], sum[c + 7]));
+          for (int c = 0; c < 16; c += 4)
+            *reinterpret_cast<uint4*>(dst + 2 * c) =
+                make_uint4(pack_bf16x2(sum2[c].x, sum2[c].y), pack_bf16x2(sum2[c + 1].x, sum2[c + 1].y),
+                           pack_bf16x2(sum2[c + 2].x, sum2[c + 2].y), pack_bf16x2(sum2[c + 3].x, sum2[c + 3].y));
         } else {
 #pragma unroll
           for (int c = 0; c < 32; ++c)
-            if (c < limit) dst[c] = __float2bfloat16_rn(sum[c]);
+            if (c < limit) dst[c] = __float2bfloat16_rn((c & 1) ? sum2[c >> 1].y : sum2[c >> 1].x);
         }
       }
     }

@@ -31,18 +31,26 @@ __device__ __forceinline__ int quantize_one(float v, float scale) {
 constexpr float kRoundMagic = 12582912.f;   // 1.5 * 2^23
 constexpr float kTieGuard = 0.49995f;       // |q' - rint(q')| below this: no tie within the error bound
 
-// Short path for one value: returns the FMA result whose low byte is the code and clears `safe`
-// when the value is not provably away from a rounding tie. shifted = RN(v * inverse + 1.5 * 2^23) is
-// the exact product rounded to the nearest integer (ties to even); the second FMA gives the exact
-// product's distance from that integer. |v * inverse - v / scale| <= 127.5 * 2^-24 and the reference's
-// own rounding of v / scale moves it by as much again, so outside the guard band both round alike.
-// NaN compares false, so NaN and inf * 0 land on the exact path too.
-__device__ __forceinline__ uint32_t quantize_fast(float v, float inverse, bool& safe) {
+// Short path for two values with packed FP32 arithmetic (two IEEE-rounded lanes per instruction):
+// returns the FMA results whose low bytes are the codes and clears `safe` when a value is not
+// provably away from a rounding tie. shifted = RN(v * inverse + 1.5 * 2^23) is the exact product
+// rounded to the nearest integer (ties to even); the last FMA gives the exact product's distance
+// from that integer. |v * inverse - v / scale| <= 127.5 * 2^-24 and the reference's own rounding of
+// v / scale moves it by as much again, so outside the guard band both round alike. NaN compares
+// false, so NaN and inf * 0 land on the exact path too.
+__device__ __forceinline__ float2 quantize_fast2(float2 v, float2 inverse, bool& safe) {
+  const float2 magic = make_float2(kRoundMagic, kRoundMagic);
+  const float2 shifted = __ffma2_rn(v, inverse, magic);
+  const float2 minus_rounded = __ffma2_rn(shifted, make_float2(-1.f, -1.f), magic);   // exact
+  const float2 residual = __ffma2_rn(v, inverse, minus_rounded);
+  safe = safe && (fabsf(residual.x) < kTieGuard) && (fabsf(residual.y) < kTieGuard);
+  return shifted;
+}
+// The same test for one value (used by the repair path to find the offender).
+__device__ __forceinline__ bool away_from_tie(float v, float inverse) {
   const float shifted = __fmaf_rn(v, inverse, kRoundMagic);
-  const float rounded = __fsub_rn(shifted, kRoundMagic);
-  const float residual = __fmaf_rn(v, inverse, -rounded);
-  safe = safe && (fabsf(residual) < kTieGuard);
-  return __float_as_uint(shifted);
+  const float residual = __fmaf_rn(v, inverse, -__fsub_rn(shifted, kRoundMagic));
+  return fabsf(residual) < kTieGuard;
 }
 
 // Running maximum of |x| over packed BF16 pairs: one LOP3 and one packed max per two values. The
@@ -60,17 +68,19 @@ __device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t running, uint32_t pai
 __device__ __forceinline__ uint2 quantize_pack(const uint4& pack, float scale, float inverse) {
   const float v[8] = {bf16_lo(pack.x), bf16_hi(pack.x), bf16_lo(pack.y), bf16_hi(pack.y),
                       bf16_lo(pack.z), bf16_hi(pack.z), bf16_lo(pack.w), bf16_hi(pack.w)};
+  const float2 inverse2 = make_float2(inverse, inverse);
   uint32_t t[8];
   bool safe = true;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) t[j] = quantize_fast(v[j], inverse, safe);
+  for (int j = 0; j < 8; j += 2) {
+    const float2 shifted = quantize_fast2(make_float2(v[j], v[j + 1]), inverse2, safe);
+    t[j] = __float_as_uint(shifted.x);
+    t[j + 1] = __float_as_uint(shifted.y);
+  }
   if (!safe) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      bool mine = true;
-      quantize_fast(v[j], inverse, mine);
-      if (!mine) t[j] = static_cast<uint32_t>(quantize_one(v[j], scale));
-    }
+    for (int j = 0; j < 8; ++j)
+      if (!away_from_tie(v[j], inverse)) t[j] = static_cast<uint32_t>(quantize_one(v[j], scale));
   }
   const uint32_t lo = __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410);
   const uint32_t hi = __byte_perm(__byte_perm(t[4], t[5], 0x0040), __byte_perm(t[6], t[7], 0x0040), 0x5410);

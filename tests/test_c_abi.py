@@ -57,6 +57,8 @@ def test_arguments_are_rejected_before_any_launch(ops):
     assert lib.ci8_cutlass_channel_mm(one, one, one, one, null, one, 1, 4, 32, null) == 1
     assert lib.ci8_grouped_channel_mm(one, one, one, one, one, 4, 4, 0, null) == 1
     assert lib.ci8_decode_mm_split(one, one, one, one, null, one, 17, 4, 32, 1, 0, null) == 1
+    assert lib.ci8_q8_block_mm(one, one, one, one, one, one, 1, 4, 48, null) == 1           # k % 32
+    assert lib.ci8_q8_block_mm(one, one, one, one, one, null, 1, 4, 32, null) == 1          # null output
 
 
 def test_operator_surface_matches_the_reference(ops):
