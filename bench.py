@@ -387,7 +387,7 @@ def other_configs(ops, workloads, device, peaks):
                                        channel_mm_u8_us=ms_u8 * 1e3, with_quantize_us=ms_q * 1e3,
                                        channel_gemv_us=ms_gemv * 1e3,
                                        channel_gemv_gbs=(n * k + 2 * n + 2 * m * k + 2 * m * n) / ms_gemv / 1e6)
-    # rows between the decode kernel (M <= 16) and a full tile: weight-stream bound on the tcgen05 GEMM
+    # rows between decode and a full tile: the streaming kernel up to 64 rows, the 128-row GEMM tile beyond
     for m in (32, 64, 128):
         x = workloads.activations(m, k, gen).to(device)
         codes = torch.empty(m, k, dtype=torch.int8, device=device)

@@ -249,16 +249,16 @@ cudaError_t launch_serialized(void (*kernel)(Params...), unsigned grid, unsigned
 // Picks the split-K factor and the slab width (channels per CTA, a multiple of 16: kind::i8 takes N in
 // steps of 16 above 32) from a small time model fitted to measurements on B200, in microseconds:
 //   fixed(split) + 4 (waves - 1) + max(weight bytes / HBM rate, waves * K blocks per CTA * time per ring stage)
-// where a ring stage (slab x 128 weight bytes + the 2 KB activation tile) takes at least 0.17 us
+// where a ring stage (slab x 128 weight bytes + the 2 or 8 KB activation tile) takes at least 0.17 us
 // (barrier round trip, TMA and MMA issue) and one SM pulls at most about 75 GB/s. Split-K shortens the
 // per-CTA stream but costs a cluster launch and the shared-memory reduction. Clusters of four lose
 // a few SMs to placement (a cluster sits inside one GPC). Ties go to the smaller split and slab.
-void choose_decode_shape(int n, int k, int sms, int* split_out, int* slab_out) {
+void choose_decode_shape(int n, int k, int rows, int max_split, int sms, int* split_out, int* slab_out) {
   const int num_kb = (k + 127) / 128;
   const double hbm_us = static_cast<double>(n) * k / 6.4e6;
   double best = 1e300;
   int best_split = 1, best_slab = 128;
-  for (int split = 1; split <= 4; split *= 2) {
+  for (int split = 1; split <= max_split; split *= 2) {
     if (split > num_kb) break;
     const long long capacity = split == 4 ? (sms / 4 - 4) * 4 : split == 2 ? (sms / 2) * 2 : sms;
     const double fixed_us = split == 1 ? 4.5 : split == 2 ? 5.0 : 5.8;
@@ -266,7 +266,7 @@ void choose_decode_shape(int n, int k, int sms, int* split_out, int* slab_out) {
       const long long slabs = (n + slab - 1) / slab;
       const long long ctas = slabs * split;
       const long long waves = (ctas + capacity - 1) / capacity;
-      const double stage_bytes = slab * 128.0 + 2048.0;
+      const double stage_bytes = (slab + rows) * 128.0;
       const double stage_us = stage_bytes / 75e3 > 0.17 ? stage_bytes / 75e3 : 0.17;
       const double stream_us = static_cast<double>(waves) * ((num_kb + split - 1) / split) * stage_us;
       const double cost = fixed_us + 4.0 * (waves - 1) + (stream_us > hbm_us ? stream_us : hbm_us);
@@ -277,11 +277,11 @@ void choose_decode_shape(int n, int k, int sms, int* split_out, int* slab_out) {
   *slab_out = best_slab;
 }
 
-template <int kSplit, bool kBiased>
+template <int kSplit, bool kBiased, int kRows>
 cudaError_t launch_decode_variant(const void* a, const void* w, const DecodeParams& p, cudaStream_t stream) {
-  using Cfg = DecodeConfig<kSplit>;
+  using Cfg = DecodeConfig<kSplit, kRows>;
   static std::atomic<uint64_t> smem_done{0};
-  auto kernel = decode_w8a8_kernel<kSplit, kBiased>;
+  auto kernel = decode_w8a8_kernel<kSplit, kBiased, kRows>;
   cudaError_t err = ensure_smem(kernel, Cfg::kSmemBytes, smem_done);
   if (err != cudaSuccess) return err;
   CUtensorMap map_w, map_a;
@@ -312,10 +312,17 @@ cudaError_t launch_decode_variant(const void* a, const void* w, const DecodePara
   return cudaLaunchKernelEx(&config, kernel, map_w, map_a, p);
 }
 
+// Rows the streaming kernel takes: up to 16 with any split, up to 64 with a split of at most two
+// (the shared-memory reduce buffer grows with the rows).
+constexpr int kDecodeMaxRows = 64;
+
 template <bool kBiased>
 cudaError_t launch_decode(const void* a, const void* w, DecodeParams p, int forced_split, cudaStream_t stream) {
+  const bool wide = p.m > 16;
+  const int max_split = wide ? 2 : 4;
+  if (forced_split > max_split) return cudaErrorInvalidValue;
   int split = 1, slab = 128;
-  choose_decode_shape(p.n, p.k, sm_count(), &split, &slab);
+  choose_decode_shape(p.n, p.k, wide ? 64 : 16, max_split, sm_count(), &split, &slab);
   if (forced_split > 0) {
     split = forced_split;
     const int per = sm_count() / split > 0 ? sm_count() / split : 1;
@@ -325,10 +332,14 @@ cudaError_t launch_decode(const void* a, const void* w, DecodeParams p, int forc
   }
   if (slab < 16 || slab > 256 || slab % 16 != 0) return cudaErrorInvalidValue;   // not an instruction shape
   p.slab = slab;
+  if (wide) {
+    return split == 1 ? launch_decode_variant<1, kBiased, 64>(a, w, p, stream)
+                      : launch_decode_variant<2, kBiased, 64>(a, w, p, stream);
+  }
   switch (split) {
-    case 1: return launch_decode_variant<1, kBiased>(a, w, p, stream);
-    case 2: return launch_decode_variant<2, kBiased>(a, w, p, stream);
-    default: return launch_decode_variant<4, kBiased>(a, w, p, stream);
+    case 1: return launch_decode_variant<1, kBiased, 16>(a, w, p, stream);
+    case 2: return launch_decode_variant<2, kBiased, 16>(a, w, p, stream);
+    default: return launch_decode_variant<4, kBiased, 16>(a, w, p, stream);
   }
 }
 
@@ -548,7 +559,7 @@ int ci8_fused_channel_mm(const int8_t* a, const int8_t* w, const float* a_scale,
       !aligned(a, 16) || !aligned(w, 16) || static_cast<long long>(m) * n > INT32_MAX)
     return kInvalid;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (m <= 16 && schedule == 0) {
+  if (m <= kDecodeMaxRows && schedule == 0) {
     DecodeParams p{a, a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out),
                    nullptr, m, n, k, 0};
     return launch_decode<false>(a, w, p, 0, s);
@@ -569,7 +580,7 @@ int ci8_cutlass_channel_mm(const int8_t* a, const int8_t* w, const float* a_scal
       !aligned(w, 16) || static_cast<long long>(m) * n > INT32_MAX)
     return kInvalid;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (m <= 16) {
+  if (m <= kDecodeMaxRows) {
     DecodeParams p{a, a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out),
                    workspace, m, n, k, 0};
     return launch_decode<false>(a, w, p, 0, s);
@@ -584,7 +595,7 @@ int ci8_channel_mm(const int8_t* a, const uint8_t* w, const float* a_scale, cons
   if (!a || !w || !a_scale || !w_scale || !out || !gemm_geometry_ok(m, n, k) || !aligned(a, 16) || !aligned(w, 16))
     return kInvalid;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (m <= 16) {
+  if (m <= kDecodeMaxRows) {
     DecodeParams p{a, a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out),
                    nullptr, m, n, k, 0};
     return launch_decode<true>(a, w, p, 0, s);
@@ -686,8 +697,6 @@ int ci8_selftest_wait_timeout(unsigned deadline_us, int* gave_up, ci8_stream_t s
   return cudaGetLastError();
 }
 
-// Test hook: the decode kernel with a forced split-K factor (1, 2 or 4); weights_biased != 0
-// selects the UINT8 form. Same contract as ci8_fused_channel_mm / ci8_channel_mm with m <= 16.
 int ci8_q8_block_mm(const void* x, int8_t* a, float* sa, const int8_t* w, const void* sw, void* y, int m, int n,
                     int k, ci8_stream_t stream) {
   if (!x || !a || !sa || !w || !sw || !y || m <= 0 || n <= 0 || k <= 0 || k % 32 != 0 || k > 65536 ||
@@ -698,10 +707,12 @@ int ci8_q8_block_mm(const void* x, int8_t* a, float* sa, const int8_t* w, const 
   return launch_q8_block(x, a, sa, w, sw, y, m, n, k, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// Test hook: the streaming kernel with a forced split-K factor (1, 2 or 4; at most 2 above 16 rows);
+// weights_biased != 0 selects the UINT8 form. Same contract as ci8_fused_channel_mm / ci8_channel_mm.
 int ci8_decode_mm_split(const int8_t* a, const void* w, const float* a_scale, const void* w_scale,
                         int32_t* workspace, void* out, int m, int n, int k, int split, int weights_biased,
                         ci8_stream_t stream) {
-  if (!a || !w || !a_scale || !w_scale || !out || !gemm_geometry_ok(m, n, k) || m > 16 ||
+  if (!a || !w || !a_scale || !w_scale || !out || !gemm_geometry_ok(m, n, k) || m > kDecodeMaxRows ||
       (split != 1 && split != 2 && split != 4) || split > (k + 127) / 128 || !aligned(a, 16) || !aligned(w, 16))
     return kInvalid;
   DecodeParams p{a, a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out),

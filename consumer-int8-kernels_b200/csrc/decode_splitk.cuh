@@ -45,40 +45,50 @@ struct DecodeParams {
   int slab;                   // channels per CTA (multiple of 16, 16..256)
 };
 
-template <int kSplit>
+template <int kSplit, int kRowsT = 16>
 struct DecodeConfig {
-  static constexpr int kRows = 16;                       // activation rows per tile (M <= 16)
+  static_assert(kRowsT == 16 || kRowsT == 64, "activation tiles of 16 or 64 rows");
+  static_assert(kRowsT == 16 || kSplit <= 2, "the 64-row reduce buffer only fits for a split of two");
+  static constexpr int kRows = kRowsT;                   // activation rows per tile (M <= kRows)
   static constexpr int kBlockK = 128;
   static constexpr int kMaxSlab = 256;
-  static constexpr int kABytes = kRows * kBlockK;        // 2 KB actually loaded per stage
+  static constexpr int kABytes = kRows * kBlockK;        // activation bytes loaded per stage
   static constexpr int kMmaM = 64;                       // smallest M of the instruction
-  static constexpr int kAOperandBytes = kMmaM * kBlockK; // what the instruction reads from the tile's start on
-  // The ring is a fixed region cut into stages of slab*128 + 2 KB bytes, as many as fit (at most
+  // a 16-row tile is followed by 48 more operand rows the instruction reads (and nobody uses)
+  static constexpr int kAOperandPad = (kMmaM - kRows) * kBlockK;
+  // The ring is a fixed region cut into stages of slab*128 + kABytes, as many as fit (at most
   // kMaxStages): a narrow slab gets more, smaller stages, so the bytes in flight stay the same.
-  static constexpr int kRingBytes = (kSplit == 1 ? 6 : kSplit == 2 ? 5 : 4) * (kMaxSlab * kBlockK + kABytes);
+  static constexpr int kRingBytes =
+      kRows == 16 ? (kSplit == 1 ? 6 : kSplit == 2 ? 5 : 4) * (kMaxSlab * kBlockK + kABytes)
+                  : (kSplit == 1 ? 5 * (kMaxSlab * kBlockK + kABytes) : 150 * 1024);
   static constexpr int kMaxStages = 24;
   static constexpr int kReduceBytes = kSplit == 1 ? 0 : (kSplit - 1) * kRows * kMaxSlab * 4;
   static constexpr int kTmemColumns = 256;
-  static constexpr int kThreads = 160;                   // warps 0 and 4 epilogue, 1 MMA, 2 TMA, 3 idle
+  // Accumulator row r lives in TMEM lane 32 * (r / 16) + r % 16, and a warp reaches the lane quarter
+  // of its index modulo four. 16 rows: warps 0 and 4 run the epilogue, 1 the MMAs, 2 the TMA loads
+  // (3 idles). 64 rows: warps 0..7 run the epilogue (two per quarter), 8 the MMAs, 9 the loads.
+  static constexpr int kEpilogueWarps = kRows == 16 ? 2 : 8;
+  static constexpr int kMmaWarp = kRows == 16 ? 1 : 8;
+  static constexpr int kTmaWarp = kRows == 16 ? 2 : 9;
+  static constexpr int kThreads = kRows == 16 ? 160 : 320;
   static constexpr int kBarrierBytes = 512;
-  static constexpr int kScaleBytes = kMaxSlab * 4 + 2 * kRows * 4;   // FP32 channel scales of the slab + row sums
-  // the last stage's A operand extends kAOperandBytes past its tile: keep that inside the allocation
-  static constexpr int kSmemBytes = kRingBytes + kAOperandBytes + kReduceBytes + kBarrierBytes + kScaleBytes + 1024;
+  static constexpr int kScaleBytes = kMaxSlab * 4 + 8 * 16 * 4;   // FP32 channel scales of the slab + row sums per warp
+  static constexpr int kSmemBytes = kRingBytes + kAOperandPad + kReduceBytes + kBarrierBytes + kScaleBytes + 1024;
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
-template <int kSplit, bool kBiased>
-__global__ void __launch_bounds__(160, 1)
+template <int kSplit, bool kBiased, int kRows = 16>
+__global__ void __launch_bounds__((DecodeConfig<kSplit, kRows>::kThreads), 1)
 decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_a, const DecodeParams p) {
-  using Cfg = DecodeConfig<kSplit>;
+  using Cfg = DecodeConfig<kSplit, kRows>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
   const uint32_t smem_base = raw_addr + pad;
-  constexpr int kReduceOffset = Cfg::kRingBytes + Cfg::kAOperandBytes;
-  int32_t* reduce_buf = reinterpret_cast<int32_t*>(smem + kReduceOffset);   // [rank-1][kMaxSlab][16]: lanes (rows) adjacent
+  constexpr int kReduceOffset = Cfg::kRingBytes + Cfg::kAOperandPad;
+  int32_t* reduce_buf = reinterpret_cast<int32_t*>(smem + kReduceOffset);   // [rank-1][kMaxSlab][kRows]: rows adjacent
   uint8_t* bar_region = smem + kReduceOffset + Cfg::kReduceBytes;
   const uint32_t bar_base = smem_base + kReduceOffset + Cfg::kReduceBytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -87,7 +97,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_region + 8 * (2 * Cfg::kMaxStages + 1));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* scale_tab = reinterpret_cast<float*>(bar_region + Cfg::kBarrierBytes);          // [kMaxSlab]
-  int32_t* row_sums = reinterpret_cast<int32_t*>(scale_tab + Cfg::kMaxSlab);             // [2][16]
+  int32_t* row_sums = reinterpret_cast<int32_t*>(scale_tab + Cfg::kMaxSlab);             // [warp][16]
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const uint32_t rank = kSplit > 1 ? cluster_ctarank() : 0u;
@@ -111,7 +121,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     prefetch_tensormap(&map_w);
     prefetch_tensormap(&map_a);
   }
-  if (warp == 1) {
+  if (warp == Cfg::kMmaWarp) {
     tmem_alloc<1>(smem_u32(tmem_slot), Cfg::kTmemColumns);
     tmem_relinquish<1>();
   }
@@ -124,7 +134,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
   pdl_launch_dependents();
   pdl_wait();
 
-  if (warp == 2) {
+  if (warp == Cfg::kTmaWarp) {
     // ---------------------------------------------------------------- TMA producer
     // The whole warp runs the loop and an elected lane issues: loop state then stays in uniform
     // registers, which is where the TMA and MMA instructions take their operands from (issued
@@ -151,9 +161,9 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
       if (++stage == num_stages) { stage = 0; phase ^= 1u; }
       if (++kb == kb_end) kb = kb_begin;
     }
-  } else if (warp == 1) {
+  } else if (warp == Cfg::kMmaWarp) {
     // ---------------------------------------------------------------- MMA issuer
-    // A = activations (signed, M = 64 of which 16 rows are real), B = weights (N = slab)
+    // A = activations (signed, M = 64 of which kRows are real), B = weights (N = slab)
     const uint32_t idesc = idesc_i8(Cfg::kMmaM, p.slab, /*b_unsigned=*/kBiased);
     int stage = 0;
     uint32_t phase = 0;
@@ -175,17 +185,20 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     }
     if (ok && elect_one()) mma_commit(done_bar);
     __syncwarp();
-  } else if (warp == 0 || warp == 4) {
+  } else if (kRows == 16 ? (warp == 0 || warp == 4) : warp < 8) {
     // ---------------------------------------------------------------- epilogue warps
-    // Accumulator rows 0..15 live in TMEM lanes 0..15, which only warps 0 and 4 of the CTA can read
-    // (a warp reaches the lane quarter of its index modulo four). The two warps take alternate
-    // 32-channel chunks; lane = accumulator row = activation row, lanes 16..31 carry garbage rows.
+    // Two warps per TMEM lane quarter take alternate 32-channel chunks; lanes 0..15 of a warp are
+    // the accumulator rows 16 * quarter + lane, lanes 16..31 carry rows nobody uses.
     const int e = warp >> 2;
-    const int row = lane;
+    const int quarter = warp & 3;
+    const int row = quarter * 16 + lane;                 // meaningful for lane < 16
+    const bool real_row = lane < 16;
+    const uint32_t tmem_lanes = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    int32_t* my_row_sums = row_sums + warp * 16;
     constexpr int kMyChunks = Cfg::kMaxSlab / 64;
     if constexpr (kBiased) {
       // sum_k a[row,k] over this CTA's K range: two lanes per activation row (each warp its own copy)
-      const int r = lane >> 1, part = lane & 1;
+      const int r = quarter * 16 + (lane >> 1), part = lane & 1;
       int sum = 0;
       if (r < p.m) {
         const int k_begin = kb_begin * Cfg::kBlockK, k_end = min(kb_end * Cfg::kBlockK, p.k);
@@ -203,11 +216,11 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
         }
       }
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      if (part == 0) row_sums[e * Cfg::kRows + r] = sum;
+      if (part == 0) my_row_sums[lane >> 1] = sum;
     }
     // the scales do not depend on the accumulation: fetch them while the weights stream
     const int chunks = (p.slab + 31) / 32;
-    const float row_scale = row < p.m ? p.sa[row] : 0.f;
+    const float row_scale = (real_row && row < p.m) ? p.sa[row] : 0.f;
 #pragma unroll
     for (int i = 0; i < kMyChunks; ++i) {
       const int c = 2 * i + e;
@@ -219,7 +232,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     const bool ok = have_work ? mbar_wait(done_bar, 0u, abort_flag) : true;
     tcgen05_fence_after();
     const bool live = __all_sync(0xffffffffu, ok) && have_work;
-    const int32_t bias = (kBiased && row < Cfg::kRows) ? 128 * row_sums[e * Cfg::kRows + row] : 0;
+    const int32_t bias = (kBiased && real_row) ? 128 * my_row_sums[lane] : 0;
     const bool out_vec = (p.n % 8 == 0) && (reinterpret_cast<uintptr_t>(p.out) % 16 == 0);
     const bool ws_vec = (p.n % 4 == 0) && (reinterpret_cast<uintptr_t>(p.workspace) % 16 == 0);
 
@@ -227,7 +240,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     // one is processed; f(chunk, acc) gets the bias-corrected INT32 accumulators of 32 channels.
     auto for_each_chunk = [&](auto&& f) {
       uint32_t v[2][32];
-      if (live && e < chunks) tmem_ld_32x32(tmem_base + e * 32, v[0]);
+      if (live && e < chunks) tmem_ld_32x32(tmem_lanes + e * 32, v[0]);
 #pragma unroll
       for (int i = 0; i < kMyChunks; ++i) {
         const int chunk = 2 * i + e;
@@ -239,7 +252,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
           for (int j = 0; j < 32; ++j) cur[j] = 0u;
         }
-        if (i + 1 < kMyChunks && live && chunk + 2 < chunks) tmem_ld_32x32(tmem_base + (chunk + 2) * 32, v[(i + 1) & 1]);
+        if (i + 1 < kMyChunks && live && chunk + 2 < chunks) tmem_ld_32x32(tmem_lanes + (chunk + 2) * 32, v[(i + 1) & 1]);
         int32_t acc[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = static_cast<int32_t>(cur[j]) - bias;
@@ -252,7 +265,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
         // push this CTA's partials into the leader's reduce buffer: [rank-1][channel][row]
         const uint32_t remote = map_to_cta(smem_u32(reduce_buf), 0);
         for_each_chunk([&](int chunk, int32_t (&acc)[32]) {
-          if (row < Cfg::kRows) {
+          if (real_row) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const uint32_t offset = (((rank - 1) * Cfg::kMaxSlab + chunk * 32 + j) * Cfg::kRows + row) * 4;
@@ -267,7 +280,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     if (rank == 0) {
       for_each_chunk([&](int chunk, int32_t (&acc)[32]) {
         if constexpr (kSplit > 1) {
-          if (row < Cfg::kRows) {
+          if (real_row) {
 #pragma unroll
             for (int r = 0; r < kSplit - 1; ++r)
 #pragma unroll
@@ -291,7 +304,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
           packed[j >> 1] = *reinterpret_cast<uint32_t*>(&lo);
           packed[(j >> 1) + 1] = *reinterpret_cast<uint32_t*>(&hi);
         }
-        if (row < p.m) {
+        if (real_row && row < p.m) {
           __nv_bfloat16* dst = p.out + static_cast<size_t>(row) * p.n + c0;
           if (out_vec && limit == 32) {
 #pragma unroll
@@ -320,14 +333,14 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     }
   }
   if constexpr (kSplit > 1) {
-    if (warp != 0 && warp != 4) {   // the epilogue warps passed the cluster rendezvous above
+    if (!(kRows == 16 ? (warp == 0 || warp == 4) : warp < 8)) {   // the epilogue warps passed the cluster rendezvous above
       cluster_arrive();
       cluster_wait();
     }
   }
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == Cfg::kMmaWarp) {
     tcgen05_fence_after();
     tmem_dealloc<1>(tmem_base, Cfg::kTmemColumns);
   }

@@ -115,8 +115,9 @@ int ci8_fused_channel_mm_gather(const int8_t* a, const int8_t* w, const float* a
                                 const void* w_scale, void* const* gathered, int world, int rank,
                                 int m, int n_shard, int k, int schedule, ci8_stream_t stream);
 
-/* The decode (m <= 16) kernel behind ci8_fused_channel_mm / ci8_cutlass_channel_mm /
- * ci8_channel_mm with the split-K factor forced to 1, 2 or 4 instead of chosen from the shape.
+/* The streaming (m <= 64) kernel behind ci8_fused_channel_mm / ci8_cutlass_channel_mm /
+ * ci8_channel_mm with the split-K factor forced to 1, 2 or 4 (1 or 2 for m > 16) instead of chosen
+ * from the shape.
  * No counterpart in the reference; it exists so that tests can show the result does not depend
  * on the split. weights_biased != 0: w is UINT8 code+128. workspace may be NULL. */
 int ci8_decode_mm_split(const int8_t* a, const void* w, const float* a_scale, const void* w_scale,

@@ -56,7 +56,8 @@ def test_arguments_are_rejected_before_any_launch(ops):
     assert lib.ci8_channel_gemv(one, one, one, one, 1, 4, 24, null) == 1       # k % 16
     assert lib.ci8_cutlass_channel_mm(one, one, one, one, null, one, 1, 4, 32, null) == 1
     assert lib.ci8_grouped_channel_mm(one, one, one, one, one, 4, 4, 0, null) == 1
-    assert lib.ci8_decode_mm_split(one, one, one, one, null, one, 17, 4, 32, 1, 0, null) == 1
+    assert lib.ci8_decode_mm_split(one, one, one, one, null, one, 65, 4, 32, 1, 0, null) == 1     # m > 64
+    assert lib.ci8_decode_mm_split(one, one, one, one, null, one, 17, 4, 512, 4, 0, null) == 1    # split 4 above 16 rows
     assert lib.ci8_q8_block_mm(one, one, one, one, one, one, 1, 4, 48, null) == 1           # k % 32
     assert lib.ci8_q8_block_mm(one, one, one, one, one, null, 1, 4, 32, null) == 1          # null output
 
