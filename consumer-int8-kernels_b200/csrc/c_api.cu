@@ -245,7 +245,7 @@ cudaError_t launch_serialized(void (*kernel)(Params...), unsigned grid, unsigned
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
-// ------------------------------------------------------------------ decode (M <= 16) launch
+// ------------------------------------------------------------------ streaming-kernel (M <= 64) launch
 // Picks the split-K factor and the slab width (channels per CTA, a multiple of 16: kind::i8 takes N in
 // steps of 16 above 32) from a small time model fitted to measurements on B200, in microseconds:
 //   fixed(split) + 4 (waves - 1) + max(weight bytes / HBM rate, waves * K blocks per CTA * time per ring stage)

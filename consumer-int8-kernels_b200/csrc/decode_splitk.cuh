@@ -1,18 +1,19 @@
-// Small-M (<= 16 rows) W8A8 linear for decode: an HBM-streaming kernel.
+// Small-M (<= 64 rows) W8A8 linear for decode and small batches: an HBM-streaming kernel.
 //
 // The weight matrix W [N,K] is read exactly once. One CTA owns a slab of C <= 256 output channels
 // (a multiple of 16) and streams it through a deep TMA ring; the host chooses C and the split-K
 // factor so that the CTAs fill the SMs in one wave. Per 128-byte K block a ring stage holds the
-// C x 128 weight tile and the 16 x 128 tile of (zero-padded) activation rows. The MMA is
-// tcgen05.mma kind::i8 with M = 64, N = C: the activations are the M side — only accumulator rows
-// 0..15 mean anything; rows 16..63 of the A operand are whatever shared memory follows the 2 KB
-// activation tile (integer garbage that lands in accumulator rows nobody reads) — and the weights
-// are the N side. Measured on B200, one such instruction (K = 32) takes about 24-33 cycles for
-// N <= 64 and N/2 cycles from N = 128 up, so four of them per stage stay far below the time the
-// stage's bytes take to arrive.
+// C x 128 weight tile and the kRows x 128 tile of (zero-padded) activation rows, kRows = 16 or 64.
+// The MMA is tcgen05.mma kind::i8 with M = 64, N = C: the activations are the M side and the
+// weights the N side. With the 16-row tile only accumulator rows 0..15 mean anything; rows 16..63
+// of the A operand are whatever shared memory follows the 2 KB activation tile (integer garbage
+// that lands in accumulator rows nobody reads). Measured on B200, one such instruction (K = 32)
+// takes about 24-33 cycles for N <= 64 and N/2 cycles from N = 128 up, so four of them per stage
+// stay far below the time the stage's bytes take to arrive.
 //
-// Warp roles: warp 2 issues the TMA loads, warp 1 the MMAs, warps 0 and 4 run the epilogue
-// (accumulator rows 0..15 are TMEM lanes 0..15, which only warps 0 and 4 can read). The producer
+// Warp roles (16-row tile): warp 2 issues the TMA loads, warp 1 the MMAs, warps 0 and 4 run the
+// epilogue (accumulator rows 0..15 are TMEM lanes 0..15, which only warps 0 and 4 can read); the
+// 64-row tile has rows in every lane quarter and uses warps 0..7 for the epilogue. The producer
 // and MMA loops are executed by their whole warp with one elected lane issuing: the loop state
 // then lives in uniform registers, which is where TMA and MMA instructions take their operands;
 // issued from a single thread inside a divergent branch every instruction paid tens of cycles of

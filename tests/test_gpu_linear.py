@@ -165,7 +165,7 @@ def test_worst_case_accumulator_magnitude(ops):
         assert_bit_equal(out[:rows], want[:rows], "decode biased out")
 
 
-# ------------------------------------------------------------------ decode kernel (M <= 16)
+# ------------------------------------------------------------------ streaming kernel (M <= 64)
 DECODE_CASES = [(1, 128, 128), (1, 128, 512), (4, 256, 512), (16, 240, 1024), (8, 132, 544), (3, 37, 128),
                 (16, 5120, 5120), (5, 1000, 17408), (2, 34816, 320),
                 # 17..64 rows: the 64-row activation tile (every TMEM lane quarter holds real rows)
