@@ -46,11 +46,17 @@ struct DecodeParams {
   int slab;                   // channels per CTA (multiple of 16, 16..256)
 };
 
-template <int kSplit, int kRowsT = 16>
+// kRowsT: rows of the activation tile in shared memory (16 or 64). kDataRowsT: distinct rows in it
+// (M <= kDataRowsT). <64, 16> is the replicated form: the 16-row box is loaded four times, so every
+// TMEM lane quarter holds a copy of the 16 result rows and eight warps share the epilogue's chunks.
+template <int kSplit, int kRowsT = 16, int kDataRowsT = kRowsT>
 struct DecodeConfig {
   static_assert(kRowsT == 16 || kRowsT == 64, "activation tiles of 16 or 64 rows");
-  static_assert(kRowsT == 16 || kSplit <= 2, "the 64-row reduce buffer only fits for a split of two");
-  static constexpr int kRows = kRowsT;                   // activation rows per tile (M <= kRows)
+  static_assert(kDataRowsT == 16 || (kDataRowsT == 64 && kRowsT == 64), "16 or 64 distinct rows");
+  static_assert(kDataRowsT == 16 || kSplit <= 2, "the 64-row reduce buffer only fits for a split of two");
+  static constexpr int kRows = kRowsT;                   // activation rows per tile
+  static constexpr int kDataRows = kDataRowsT;           // distinct rows (the TMA box)
+  static constexpr bool kReplicated = kRowsT != kDataRowsT;
   static constexpr int kBlockK = 128;
   static constexpr int kMaxSlab = 256;
   static constexpr int kABytes = kRows * kBlockK;        // activation bytes loaded per stage
@@ -61,9 +67,10 @@ struct DecodeConfig {
   // kMaxStages): a narrow slab gets more, smaller stages, so the bytes in flight stay the same.
   static constexpr int kRingBytes =
       kRows == 16 ? (kSplit == 1 ? 6 : kSplit == 2 ? 5 : 4) * (kMaxSlab * kBlockK + kABytes)
-                  : (kSplit == 1 ? 5 * (kMaxSlab * kBlockK + kABytes) : 150 * 1024);
+      : kReplicated ? (kSplit == 1 ? 5 : kSplit == 2 ? 4 : 3) * (kMaxSlab * kBlockK + kABytes)
+                    : (kSplit == 1 ? 5 * (kMaxSlab * kBlockK + kABytes) : 150 * 1024);
   static constexpr int kMaxStages = 24;
-  static constexpr int kReduceBytes = kSplit == 1 ? 0 : (kSplit - 1) * kRows * kMaxSlab * 4;
+  static constexpr int kReduceBytes = kSplit == 1 ? 0 : (kSplit - 1) * kDataRows * kMaxSlab * 4;
   static constexpr int kTmemColumns = 256;
   // Accumulator row r lives in TMEM lane 32 * (r / 16) + r % 16, and a warp reaches the lane quarter
   // of its index modulo four. 16 rows: warps 0 and 4 run the epilogue, 1 the MMAs, 2 the TMA loads
@@ -78,11 +85,11 @@ struct DecodeConfig {
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
-template <int kSplit, bool kBiased, int kRows = 16>
-__global__ void __launch_bounds__((DecodeConfig<kSplit, kRows>::kThreads), 1)
+template <int kSplit, bool kBiased, int kRows = 16, int kDataRows = kRows>
+__global__ void __launch_bounds__((DecodeConfig<kSplit, kRows, kDataRows>::kThreads), 1)
 decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_a, const DecodeParams p) {
-  using Cfg = DecodeConfig<kSplit, kRows>;
+  using Cfg = DecodeConfig<kSplit, kRows, kDataRows>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -156,7 +163,9 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
         mbar_arrive_expect_tx(full_bar(stage), tx);
         const uint32_t w_dst = smem_base + stage * stage_bytes;
         tma_load_2d(w_dst, &map_w, kb * Cfg::kBlockK, n0, full_bar(stage));
-        tma_load_2d(w_dst + w_bytes, &map_a, kb * Cfg::kBlockK, 0, full_bar(stage));
+#pragma unroll
+        for (int copy = 0; copy < Cfg::kRows / Cfg::kDataRows; ++copy)   // the same box into every lane quarter's rows
+          tma_load_2d(w_dst + w_bytes + copy * Cfg::kDataRows * Cfg::kBlockK, &map_a, kb * Cfg::kBlockK, 0, full_bar(stage));
       }
       __syncwarp();
       if (++stage == num_stages) { stage = 0; phase ^= 1u; }
@@ -192,14 +201,17 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     // the accumulator rows 16 * quarter + lane, lanes 16..31 carry rows nobody uses.
     const int e = warp >> 2;
     const int quarter = warp & 3;
-    const int row = quarter * 16 + lane;                 // meaningful for lane < 16
+    const int row = Cfg::kReplicated ? lane : quarter * 16 + lane;   // meaningful for lane < 16
+    // chunks of this warp: first, first + stride, ... (the replicated form spreads them over all eight warps)
+    constexpr int kChunkStride = Cfg::kReplicated ? 8 : 2;
+    const int first_chunk = Cfg::kReplicated ? quarter * 2 + e : e;
     const bool real_row = lane < 16;
     const uint32_t tmem_lanes = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     int32_t* my_row_sums = row_sums + warp * 16;
-    constexpr int kMyChunks = Cfg::kMaxSlab / 64;
+    constexpr int kMyChunks = Cfg::kMaxSlab / 32 / kChunkStride;
     if constexpr (kBiased) {
       // sum_k a[row,k] over this CTA's K range: two lanes per activation row (each warp its own copy)
-      const int r = quarter * 16 + (lane >> 1), part = lane & 1;
+      const int r = (Cfg::kReplicated ? 0 : quarter * 16) + (lane >> 1), part = lane & 1;
       int sum = 0;
       if (r < p.m) {
         const int k_begin = kb_begin * Cfg::kBlockK, k_end = min(kb_end * Cfg::kBlockK, p.k);
@@ -224,7 +236,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     const float row_scale = (real_row && row < p.m) ? p.sa[row] : 0.f;
 #pragma unroll
     for (int i = 0; i < kMyChunks; ++i) {
-      const int c = 2 * i + e;
+      const int c = kChunkStride * i + first_chunk;
       const int channel = n0 + c * 32 + lane;
       scale_tab[c * 32 + lane] = (c * 32 + lane < p.slab && channel < p.n) ? __bfloat162float(p.sw[channel]) : 0.f;
     }
@@ -241,10 +253,10 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     // one is processed; f(chunk, acc) gets the bias-corrected INT32 accumulators of 32 channels.
     auto for_each_chunk = [&](auto&& f) {
       uint32_t v[2][32];
-      if (live && e < chunks) tmem_ld_32x32(tmem_lanes + e * 32, v[0]);
+      if (live && first_chunk < chunks) tmem_ld_32x32(tmem_lanes + first_chunk * 32, v[0]);
 #pragma unroll
       for (int i = 0; i < kMyChunks; ++i) {
-        const int chunk = 2 * i + e;
+        const int chunk = kChunkStride * i + first_chunk;
         if (chunk >= chunks) break;
         uint32_t (&cur)[32] = v[i & 1];
         if (live) {
@@ -253,7 +265,8 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
           for (int j = 0; j < 32; ++j) cur[j] = 0u;
         }
-        if (i + 1 < kMyChunks && live && chunk + 2 < chunks) tmem_ld_32x32(tmem_lanes + (chunk + 2) * 32, v[(i + 1) & 1]);
+        if (i + 1 < kMyChunks && live && chunk + kChunkStride < chunks)
+          tmem_ld_32x32(tmem_lanes + (chunk + kChunkStride) * 32, v[(i + 1) & 1]);
         int32_t acc[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = static_cast<int32_t>(cur[j]) - bias;
@@ -269,7 +282,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
           if (real_row) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const uint32_t offset = (((rank - 1) * Cfg::kMaxSlab + chunk * 32 + j) * Cfg::kRows + row) * 4;
+              const uint32_t offset = (((rank - 1) * Cfg::kMaxSlab + chunk * 32 + j) * Cfg::kDataRows + row) * 4;
               asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + offset), "r"(acc[j]) : "memory");
             }
           }
@@ -285,7 +298,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
 #pragma unroll
             for (int r = 0; r < kSplit - 1; ++r)
 #pragma unroll
-              for (int j = 0; j < 32; ++j) acc[j] += reduce_buf[(r * Cfg::kMaxSlab + chunk * 32 + j) * Cfg::kRows + row];
+              for (int j = 0; j < 32; ++j) acc[j] += reduce_buf[(r * Cfg::kMaxSlab + chunk * 32 + j) * Cfg::kDataRows + row];
           }
         }
         const int c0 = n0 + chunk * 32;                     // first output channel of this chunk
