@@ -372,11 +372,14 @@ def other_configs(ops, workloads, device, peaks):
     copies = [w.to(device) for _ in range(4)]
     copies_u8 = [(w.to(torch.int16) + 128).to(torch.uint8).to(device) for _ in range(2)]
     sw = w_scale.to(device)
+    # one set of buffers for every M (views of their first rows), so that the four cases do not differ in
+    # where the allocator happened to place them
+    x16 = workloads.activations(16, k, gen).to(device)
+    codes16 = torch.empty(16, k, dtype=torch.int8, device=device)
+    scales16 = torch.empty(16, device=device)
+    out16 = torch.empty(16, n, dtype=torch.bfloat16, device=device)
     for m in (1, 4, 8, 16):
-        x = workloads.activations(m, k, gen).to(device)
-        codes = torch.empty(m, k, dtype=torch.int8, device=device)
-        scales = torch.empty(m, device=device)
-        out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+        x, codes, scales, out = x16[:m], codes16[:m], scales16[:m], out16[:m]
         ops.quantize_rows(x, codes, scales)
         nbytes = n * k + 2 * n + m * k + 4 * m + 2 * m * n
         ms = _time_graph(lambda i: ops.fused_channel_mm(codes, copies[i % 4], scales, sw, out, 0), 40)
