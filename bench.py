@@ -442,6 +442,23 @@ def other_configs(ops, workloads, device, peaks):
     results["silu_mul_quantize_4096x17408"] = dict(us=ms * 1e3, gbs=(5 * m * k + 4 * m) / ms / 1e6,
                                                    frac_hbm=(5 * m * k + 4 * m) / ms / 1e6 / hbm)
     del gate_up, codes
+    # the gate/up GEMM with the SwiGLU in its epilogue, then the row quantizer on its [4096, 17408] output:
+    # the fused replacement of prefill_gate_up + silu_mul_quantize
+    from consumer_int8.quantization import interleave_gate_up
+    m, n, k = 4096, 34816, 5120
+    w, w_scale = workloads.weights(n, k, gen)
+    wi, swi = interleave_gate_up(w.to(device), w_scale.to(device))
+    x = workloads.activations(m, k, gen).to(device)
+    codes = torch.empty(m, k, dtype=torch.int8, device=device)
+    scales = torch.empty(m, device=device)
+    ops.quantize_rows(x, codes, scales)
+    hidden = torch.empty(m, n // 2, dtype=torch.bfloat16, device=device)
+    codes2 = torch.empty(m, n // 2, dtype=torch.int8, device=device)
+    scales2 = torch.empty(m, device=device)
+    ms = _time_graph(lambda i: ops.gate_up_silu_mm(codes, wi, scales, swi, hidden), 20)
+    ms_q = _time_graph(lambda i: ops.quantize_rows(hidden, codes2, scales2), 20)
+    results["gate_up_silu_mm_4096"] = dict(gemm_ms=ms, tops=2.0 * m * n * k / ms / 1e9, quantize_us=ms_q * 1e3)
+    del wi, swi, x, codes, hidden, codes2
     spec = WORKLOADS["grouped"]
     m, n, groups = spec["m"], spec["n"], spec["groups"]
     inputs = workloads.grouped_inputs(m, n, groups, seed=0)

@@ -65,3 +65,17 @@ def quantize_group32(weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
 
 def dequantize_group32(codes: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     return codes.float() * scale.repeat_interleave(GROUP, dim=1)[:, : codes.shape[1]]
+
+
+def interleave_gate_up(weight: torch.Tensor, scale: torch.Tensor, block: int = 128):
+    """Row order for ``ops.gate_up_silu_mm``: the fused gate/up projection ``[gate(I) | up(I)]`` rows
+    (the layout ``silu_mul`` reads, reference csrc/silu_quant.cu:64-88) are regrouped so that rows
+    ``[2*block*t, 2*block*t + block)`` are gate channels ``[block*t, block*(t+1))`` and the next
+    ``block`` rows the up channels of the same range; ``scale`` is permuted alike. No counterpart in
+    the reference (it keeps the two operators separate); done once, offline, per weight matrix."""
+    n = weight.shape[0]
+    inner = n // 2
+    assert n % 2 == 0 and inner % block == 0 and scale.shape[0] == n
+    index = torch.arange(inner, device=weight.device).reshape(inner // block, 1, block)
+    order = torch.cat([index, index + inner], dim=1).reshape(-1)
+    return weight[order].contiguous(), scale[order].contiguous()

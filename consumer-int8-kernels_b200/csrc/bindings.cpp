@@ -244,6 +244,32 @@ void boxed_grouped_mm(StableIValue* stack, uint64_t, uint64_t) {
                                   groups, stream_for(device)));
 }
 
+// Additive operator: gate/up projection with the SwiGLU in the GEMM epilogue; the same bits as
+// fused_channel_mm followed by silu_mul. w / w_scale rows are gate and up interleaved in blocks of 128.
+void boxed_gate_up_silu_mm(StableIValue* stack, uint64_t, uint64_t) {
+  auto a = to<Tensor>(stack[0]), w = to<Tensor>(stack[1]), sa = to<Tensor>(stack[2]);
+  auto sw = to<Tensor>(stack[3]), out = to<Tensor>(stack[4]);
+  const int device = a.get_device_index();
+  check(a, ScalarType::Char, device);
+  check(w, ScalarType::Char, device);
+  check(sa, ScalarType::Float, device);
+  check(sw, ScalarType::BFloat16, device);
+  check(out, ScalarType::BFloat16, device);
+  STD_TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && sa.dim() == 1 && sw.dim() == 1 && out.dim() == 2,
+                  "Expected INT8 a[M,K], INT8 w[N,K], FP32 a_scale[M], BF16 w_scale[N], BF16 out[M,N/2]");
+  const int64_t m = a.size(0), k = a.size(1), n = w.size(0);
+  STD_TORCH_CHECK(m > 0 && n > 0 && n % 256 == 0 && k > 0 && k % 32 == 0 && k <= 65536 && w.size(1) == k &&
+                      sa.size(0) == m && sw.size(0) == n && out.size(0) == m && out.size(1) == n / 2,
+                  "Invalid gate/up GEMM geometry");
+  STD_TORCH_CHECK(a.numel() <= kIntMax && w.numel() <= kIntMax && m * n <= kIntMax, "Matrix too large");
+  STD_TORCH_CHECK(address(a) % 16 == 0 && address(w) % 16 == 0 && address(out) % 16 == 0,
+                  "Matrix operands must be 16-byte aligned");
+  torch::stable::accelerator::DeviceGuard guard(device);
+  launched(ci8_gate_up_silu_mm(static_cast<int8_t*>(a.data_ptr()), static_cast<int8_t*>(w.data_ptr()),
+                               static_cast<float*>(sa.data_ptr()), sw.data_ptr(), out.data_ptr(), m, n, k,
+                               stream_for(device)));
+}
+
 // Additive operator: this rank's output-channel shard of fused_channel_mm, written straight into
 // block `rank` of every rank's gathered buffer [world, M, N/world] (peer-mapped symmetric memory).
 // peer_ptrs is a CPU INT64 tensor holding the device address of every rank's buffer.
@@ -295,6 +321,7 @@ STABLE_TORCH_LIBRARY(consumer_int8, m) {
   m.def("channel_gemv(Tensor x, Tensor w, Tensor scale, Tensor(a!) out) -> ()");
   m.def("cutlass_channel_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) workspace, Tensor(b!) out) -> ()");
   m.def("grouped_channel_mm(Tensor codes, Tensor w, Tensor scales, Tensor w_scale, Tensor(a!) out) -> ()");
+  m.def("gate_up_silu_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) out) -> ()");
   m.def("fused_channel_mm_gather(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) gathered, Tensor peer_ptrs, int rank, int schedule=0) -> ()");
 }
 STABLE_TORCH_LIBRARY_IMPL(consumer_int8, CUDA, m) {
@@ -308,6 +335,7 @@ STABLE_TORCH_LIBRARY_IMPL(consumer_int8, CUDA, m) {
   m.impl("channel_gemv", &boxed_gemv);
   m.impl("cutlass_channel_mm", &boxed_cutlass_mm);
   m.impl("grouped_channel_mm", &boxed_grouped_mm);
+  m.impl("gate_up_silu_mm", &boxed_gate_up_silu_mm);
   m.impl("fused_channel_mm_gather", &boxed_fused_mm_gather);
 }
 extern "C" PyObject* PyInit__C() {

@@ -140,8 +140,11 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   // wider tile. A schedule can force the width; the biased form keeps 240 channels + 16 ones rows,
   // unsliced; the gathering form needs whole 64-column boxes (256 or 192 wide, slices of 128 or 64).
   int tile_n = 256, split = 1;
+  p.out_n = kMode == kModeSwiGLU ? p.n / 2 : p.n;
   if (kMode == kModeBiased) {
     tile_n = Cfg::kChannelsPerTile;
+  } else if (kMode == kModeSwiGLU) {
+    tile_n = 256;   // a tile is 128 gate channels and their 128 up channels: whole, unsliced tiles only
   } else {
     const bool forced = p.tile_n > 0 && num_outputs <= 1;
     double best = 1e300;
@@ -189,17 +192,17 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
     outputs = local_only;
     num_outputs = 1;
   }
-  bool tile_stores = kMode != kModeBiased && p.n % 8 == 0 && num_outputs <= kMaxOutputs;
+  bool tile_stores = kMode != kModeBiased && p.out_n % 8 == 0 && num_outputs <= kMaxOutputs;
   for (int d = 0; d < num_outputs; ++d) tile_stores = tile_stores && aligned(outputs[d], 16);
   p.num_outputs = 0;
   if (tile_stores) {
     for (int d = 0; d < num_outputs; ++d) {
-      err = make_output_map(&out_maps.map[d], outputs[d], p.m, p.n);
+      err = make_output_map(&out_maps.map[d], outputs[d], p.m, p.out_n);
       if (err != cudaSuccess) return err;
     }
     p.num_outputs = num_outputs;
-  } else if (num_outputs != 1) {
-    return cudaErrorInvalidValue;   // several destinations need the tile-store path
+  } else if (num_outputs != 1 || kMode == kModeSwiGLU) {
+    return cudaErrorInvalidValue;   // several destinations, and the SwiGLU form, need the tile-store path
   }
 
   const long long tiles = p.total_items;
@@ -708,6 +711,17 @@ int ci8_selftest_wait_timeout(unsigned deadline_us, int* gave_up, ci8_stream_t s
   wait_timeout_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<unsigned long long>(deadline_us) * 1000ull, gave_up);
   return cudaGetLastError();
+}
+
+int ci8_gate_up_silu_mm(const int8_t* a, const int8_t* w, const float* a_scale, const void* w_scale, void* out, int m,
+                        int n, int k, ci8_stream_t stream) {
+  if (!a || !w || !a_scale || !w_scale || !out || !gemm_geometry_ok(m, n, k) || n % 256 != 0 || !aligned(a, 16) ||
+      !aligned(w, 16) || !aligned(out, 16) || static_cast<long long>(m) * n > INT32_MAX)
+    return kInvalid;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
+               m, n, k, 1, 0, 0, 0, 0, 0, 0};
+  return m > 128 ? launch_gemm<2, kModeSwiGLU>(a, w, p, s) : launch_gemm<1, kModeSwiGLU>(a, w, p, s);
 }
 
 int ci8_q8_block_mm(const void* x, int8_t* a, float* sa, const int8_t* w, const void* sw, void* y, int m, int n,

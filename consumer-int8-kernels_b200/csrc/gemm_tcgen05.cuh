@@ -28,14 +28,22 @@
 //                   group's INT32 accumulator is converted, scaled and added in FP32 in
 //                   ascending group order (separate multiply and add), then the channel
 //                   scale is applied (grouped_channel_mm)
+//   kModeSwiGLU     the gate/up projection with the SwiGLU fused into the epilogue: the weight rows
+//                   are interleaved in blocks of 128 (tile t holds gate channels [128t, 128t+128) in
+//                   its first 128 rows and the matching up channels in the other 128), so a tile's
+//                   accumulator has a gate half and an up half; the epilogue rounds both to BF16
+//                   exactly as kModeFused would have written them, and stores
+//                   bf16(silu(gate) * up) [M, N/2] — bit-identical to fused_channel_mm followed
+//                   by silu_mul, without the [M, N] round trip through HBM
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include "quantize.cuh"
 #include "sm100_ptx.cuh"
 
 namespace ci8 {
 
-enum GemmMode { kModeFused = 0, kModeWorkspace = 1, kModeBiased = 2, kModeGrouped = 3 };
+enum GemmMode { kModeFused = 0, kModeWorkspace = 1, kModeBiased = 2, kModeGrouped = 3, kModeSwiGLU = 4 };
 
 constexpr int kMaxOutputs = 8;   // destinations of one output tile (this GPU + up to 7 peers)
 
@@ -56,6 +64,7 @@ struct GemmParams {
   int full_tiles;             // work items [0, full_tiles) are whole tiles (the complete waves)
   int split;                  // each tile of the last, partial wave is cut into `split` column slices
   int total_items;            // full_tiles + (tiles - full_tiles) * split
+  int out_n;                  // columns of the output matrix: n, or n / 2 for kModeSwiGLU
 };
 
 // Tensor maps of the output destinations: BF16 [M,N] matrices, boxes of 64 columns x 32 rows.
@@ -330,6 +339,66 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
           tmem_ld_wait();
           bias = static_cast<int32_t>(ones[0]) * 128;
         }
+        if constexpr (kMode == kModeSwiGLU) {
+          // Accumulator columns [0,128) are gate channels, [128,256) the matching up channels. Two output
+          // boxes of 64 columns per tile; each half box needs 32 gate and 32 up accumulators.
+          const int h0_tile = nt * (Cfg::kTileN / 2);       // first output column of this tile
+#pragma unroll
+          for (int boxi = 0; boxi < 2; ++boxi) {
+            const int c0 = h0_tile + boxi * 64;             // first output column of this box
+            const bool store_box = c0 < p.out_n;
+            uint8_t* box = my_staging + (store_iter % Cfg::kStoreBufs) * Cfg::kStoreBoxBytes;
+            if (store_box && store_iter >= Cfg::kStoreBufs) {
+              if (lane == 0) tma_store_wait_read<Cfg::kStoreBufs - 1>();
+              __syncwarp();
+            }
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const int gate_col = boxi * 64 + half * 32;   // accumulator column of the first gate value
+              uint32_t vg[32], vu[32];
+              tmem_ld_32x32(taddr + gate_col, vg);
+              tmem_ld_32x32(taddr + Cfg::kTileN / 2 + gate_col, vu);
+              tmem_ld_wait_for(vg);
+              tmem_ld_wait_for(vu);
+              if (!store_box) continue;
+              // channel scales: lane j holds those of gate column j and up column j of this half box
+              const int gate_n = n0 + gate_col + lane, up_n = gate_n + Cfg::kTileN / 2;
+              const float my_gate_sw = gate_n < p.n ? __bfloat162float(p.sw[gate_n]) : 0.f;
+              const float my_up_sw = up_n < p.n ? __bfloat162float(p.sw[up_n]) : 0.f;
+              uint32_t packed[16];
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                float h[2];
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                  const float gs = __shfl_sync(0xffffffffu, my_gate_sw, j + t);
+                  const float us = __shfl_sync(0xffffffffu, my_up_sw, j + t);
+                  // what fused_channel_mm would have written (BF16), read back as silu_mul would
+                  const float gate = __bfloat162float(__float2bfloat16_rn(
+                      __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(vg[j + t])), row_scale), gs)));
+                  const float up = __bfloat162float(__float2bfloat16_rn(
+                      __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int32_t>(vu[j + t])), row_scale), us)));
+                  h[t] = swiglu_one(gate, up);
+                }
+                packed[j >> 1] = pack_bf16x2(h[0], h[1]);
+              }
+              uint4* row_base = reinterpret_cast<uint4*>(box + lane * 128);
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+                row_base[(half * 4 + c) ^ (lane & 7)] =
+                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            }
+            if (store_box) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0 && row0 < p.m) {
+                tma_store_2d(&out_maps.map[0], smem_u32(box), c0, row0);
+                tma_store_commit();
+              }
+              ++store_iter;
+            }
+          }
+        } else {
         const bool last_group = g + 1 == p.groups;
 #pragma unroll
         for (int chunk = 0; chunk < kChunks; ++chunk) {
@@ -434,6 +503,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
             }
             ++store_iter;
           }
+        }
         }
         // this warp is done with the accumulator buffer
         tcgen05_fence_before();

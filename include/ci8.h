@@ -92,6 +92,17 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
                            const void* w_scale, void* out, int m, int n, int groups,
                            ci8_stream_t stream);
 
+/* The gate/up projection with the SwiGLU fused into its epilogue. No single counterpart in the
+ * reference: it replaces fused_channel_mm (csrc/fused_mm.cu:66-93) followed by silu_mul
+ * (csrc/silu_quant.cu:64-88) and produces the same bits as that pair, without writing and re-reading
+ * the [m, n] BF16 intermediate. w INT8 [n, k] and w_scale BF16 [n] hold gate and up rows interleaved
+ * in blocks of 128: rows [256t, 256t+128) are gate channels [128t, 128t+128), rows [256t+128, 256t+256)
+ * the up channels of the same range (consumer_int8.quantization.interleave_gate_up builds this order
+ * from the [gate | up] layout). out BF16 [m, n/2] = bf16(silu(gate) * up) with gate and up rounded to
+ * BF16 first, as the unfused pair does. n % 256 == 0, k % 32 == 0; a, w and out 16-byte aligned. */
+int ci8_gate_up_silu_mm(const int8_t* a, const int8_t* w, const float* a_scale, const void* w_scale,
+                        void* out, int m, int n, int k, ci8_stream_t stream);
+
 /* Replaces q8_block_int8 (reference benchmarks/cuda/q8_block_int8.cu:150-160, a raw C entry point
  * bound with ctypes by benchmarks/benchmark_q8_block_int8.py:36-39; same argument order). Block-32
  * (GGUF Q8_0) W8A8: x BF16 [m,k] is quantized per 32 values into a INT8 [m,k] with sa FP32
