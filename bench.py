@@ -386,8 +386,13 @@ def other_configs(ops, workloads, device, peaks):
         ms_u8 = _time_graph(lambda i: ops.channel_mm(codes, copies_u8[i % 2], scales, sw, out), 40)
         ms_q = _time_graph(lambda i: (ops.quantize_rows(x, codes, scales), ops.fused_channel_mm(codes, copies[i % 4], scales, sw, out, 0)), 40)
         ms_gemv = _time_graph(lambda i: ops.channel_gemv(x, copies[i % 4], sw, out), 20)
+        # BF16 activations in, one kernel: the quantizer runs inside the streaming kernel
+        ms_dyn = _time_graph(lambda i: ops.dynamic_channel_mm(x, copies[i % 4], sw, codes, scales, out), 40)
+        dyn_bytes = n * k + 2 * n + 2 * m * k + 2 * m * n
         results[f"decode_m{m}"] = dict(us=ms * 1e3, gbs=nbytes / ms / 1e6, frac_hbm=nbytes / ms / 1e6 / hbm,
                                        channel_mm_u8_us=ms_u8 * 1e3, with_quantize_us=ms_q * 1e3,
+                                       dynamic_us=ms_dyn * 1e3, dynamic_gbs=dyn_bytes / ms_dyn / 1e6,
+                                       dynamic_frac_hbm=dyn_bytes / ms_dyn / 1e6 / hbm,
                                        channel_gemv_us=ms_gemv * 1e3,
                                        channel_gemv_gbs=(n * k + 2 * n + 2 * m * k + 2 * m * n) / ms_gemv / 1e6)
     # rows between decode and a full tile: the streaming kernel up to 64 rows, the 128-row GEMM tile beyond

@@ -244,6 +244,34 @@ void boxed_grouped_mm(StableIValue* stack, uint64_t, uint64_t) {
                                   groups, stream_for(device)));
 }
 
+// Additive operator: quantize_rows + fused_channel_mm as one call (one kernel for decode shapes); codes and
+// scales receive what quantize_rows would write.
+void boxed_dynamic_mm(StableIValue* stack, uint64_t, uint64_t) {
+  auto x = to<Tensor>(stack[0]), w = to<Tensor>(stack[1]), sw = to<Tensor>(stack[2]);
+  auto codes = to<Tensor>(stack[3]), scales = to<Tensor>(stack[4]), out = to<Tensor>(stack[5]);
+  const int device = x.get_device_index();
+  check(x, ScalarType::BFloat16, device);
+  check(w, ScalarType::Char, device);
+  check(sw, ScalarType::BFloat16, device);
+  check(codes, ScalarType::Char, device);
+  check(scales, ScalarType::Float, device);
+  check(out, ScalarType::BFloat16, device);
+  STD_TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && sw.dim() == 1 && codes.dim() == 2 && scales.dim() == 1 && out.dim() == 2,
+                  "Expected BF16 x[M,K], INT8 w[N,K], BF16 w_scale[N], INT8 codes[M,K], FP32 scales[M], BF16 out[M,N]");
+  const int64_t m = x.size(0), k = x.size(1), n = w.size(0);
+  STD_TORCH_CHECK(m > 0 && n > 0 && n % 4 == 0 && k > 0 && k % 32 == 0 && k <= 65536 && w.size(1) == k &&
+                      sw.size(0) == n && codes.size(0) == m && codes.size(1) == k && scales.size(0) == m &&
+                      out.size(0) == m && out.size(1) == n,
+                  "Invalid dynamic GEMM geometry");
+  STD_TORCH_CHECK(x.numel() <= kIntMax && w.numel() <= kIntMax && out.numel() <= kIntMax, "Matrix too large");
+  STD_TORCH_CHECK(address(x) % 16 == 0 && address(w) % 16 == 0 && address(codes) % 16 == 0,
+                  "Matrix operands must be 16-byte aligned");
+  torch::stable::accelerator::DeviceGuard guard(device);
+  launched(ci8_dynamic_channel_mm(x.data_ptr(), static_cast<int8_t*>(w.data_ptr()), sw.data_ptr(),
+                                  static_cast<int8_t*>(codes.data_ptr()), static_cast<float*>(scales.data_ptr()),
+                                  out.data_ptr(), m, n, k, stream_for(device)));
+}
+
 // Additive operator: gate/up projection with the SwiGLU in the GEMM epilogue; the same bits as
 // fused_channel_mm followed by silu_mul. w / w_scale rows are gate and up interleaved in blocks of 128.
 void boxed_gate_up_silu_mm(StableIValue* stack, uint64_t, uint64_t) {
@@ -321,6 +349,7 @@ STABLE_TORCH_LIBRARY(consumer_int8, m) {
   m.def("channel_gemv(Tensor x, Tensor w, Tensor scale, Tensor(a!) out) -> ()");
   m.def("cutlass_channel_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) workspace, Tensor(b!) out) -> ()");
   m.def("grouped_channel_mm(Tensor codes, Tensor w, Tensor scales, Tensor w_scale, Tensor(a!) out) -> ()");
+  m.def("dynamic_channel_mm(Tensor x, Tensor w, Tensor w_scale, Tensor(a!) codes, Tensor(b!) scales, Tensor(c!) out) -> ()");
   m.def("gate_up_silu_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) out) -> ()");
   m.def("fused_channel_mm_gather(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) gathered, Tensor peer_ptrs, int rank, int schedule=0) -> ()");
 }
@@ -336,6 +365,7 @@ STABLE_TORCH_LIBRARY_IMPL(consumer_int8, CUDA, m) {
   m.impl("cutlass_channel_mm", &boxed_cutlass_mm);
   m.impl("grouped_channel_mm", &boxed_grouped_mm);
   m.impl("gate_up_silu_mm", &boxed_gate_up_silu_mm);
+  m.impl("dynamic_channel_mm", &boxed_dynamic_mm);
   m.impl("fused_channel_mm_gather", &boxed_fused_mm_gather);
 }
 extern "C" PyObject* PyInit__C() {

@@ -286,17 +286,18 @@ void choose_decode_shape(int n, int k, int rows, int max_split, int sms, int* sp
   *slab_out = best_slab;
 }
 
-template <int kSplit, bool kBiased, int kRows, int kDataRows = kRows>
+template <int kSplit, bool kBiased, int kRows, int kDataRows = kRows, bool kDynamic = false>
 cudaError_t launch_decode_variant(const void* a, const void* w, const DecodeParams& p, cudaStream_t stream) {
-  using Cfg = DecodeConfig<kSplit, kRows, kDataRows>;
+  using Cfg = DecodeConfig<kSplit, kRows, kDataRows, kDynamic>;
   static std::atomic<uint64_t> smem_done{0};
-  auto kernel = decode_w8a8_kernel<kSplit, kBiased, kRows, kDataRows>;
+  auto kernel = decode_w8a8_kernel<kSplit, kBiased, kRows, kDataRows, kDynamic>;
   cudaError_t err = ensure_smem(kernel, Cfg::kSmemBytes, smem_done);
   if (err != cudaSuccess) return err;
   CUtensorMap map_w, map_a;
   err = make_map(&map_w, w, p.n, p.k, p.slab);
   if (err != cudaSuccess) return err;
-  err = make_map(&map_a, a, p.m, p.k, Cfg::kDataRows);
+  // the dynamic form reads the BF16 activations (64-column boxes); the others the INT8 codes
+  err = kDynamic ? make_bf16_map(&map_a, p.x, p.m, p.k, 64, 16) : make_map(&map_a, a, p.m, p.k, Cfg::kDataRows);
   if (err != cudaSuccess) return err;
   const int slabs = (p.n + p.slab - 1) / p.slab;
   cudaLaunchConfig_t config = {};
@@ -711,6 +712,28 @@ int ci8_selftest_wait_timeout(unsigned deadline_us, int* gave_up, ci8_stream_t s
   wait_timeout_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<unsigned long long>(deadline_us) * 1000ull, gave_up);
   return cudaGetLastError();
+}
+
+int ci8_dynamic_channel_mm(const void* x, const int8_t* w, const void* w_scale, int8_t* codes, float* scales, void* out,
+                           int m, int n, int k, ci8_stream_t stream) {
+  if (!x || !w || !w_scale || !codes || !scales || !out || !gemm_geometry_ok(m, n, k) || !aligned(x, 16) ||
+      !aligned(codes, 16) || !aligned(w, 16) || static_cast<long long>(m) * n > INT32_MAX)
+    return kInvalid;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (m <= 16 && k <= 8192) {
+    // one kernel when the streaming kernel would run unsplit: it scans the activations for the row scales
+    // and quantizes each K block on its way into the operand tile
+    int split = 1, slab = 128;
+    choose_decode_shape(n, k, 16, 4, sm_count(), &split, &slab);
+    if (split == 1) {
+      DecodeParams p{codes, scales, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out),
+                     nullptr, m, n, k, slab, codes, scales, static_cast<const uint16_t*>(x)};
+      return launch_decode_variant<1, false, 64, 16, true>(codes, w, p, s);
+    }
+  }
+  cudaError_t err = launch_quantize(x, codes, scales, m, k, m, 0, s);
+  if (err != cudaSuccess) return err;
+  return ci8_fused_channel_mm(codes, w, scales, w_scale, out, m, n, k, 0, stream);
 }
 
 int ci8_gate_up_silu_mm(const int8_t* a, const int8_t* w, const float* a_scale, const void* w_scale, void* out, int m,

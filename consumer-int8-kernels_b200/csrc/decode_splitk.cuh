@@ -32,6 +32,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include "quantize.cuh"
 #include "sm100_ptx.cuh"
 
 namespace ci8 {
@@ -44,13 +45,22 @@ struct DecodeParams {
   int32_t* workspace;         // optional [M,N] INT32 accumulators
   int m, n, k;
   int slab;                   // channels per CTA (multiple of 16, 16..256)
+  // dynamic form only: the kernel quantizes the BF16 activations itself (sa is unused, a is written)
+  int8_t* codes_out;          // [M,K] INT8 codes, as quantize_rows would write them
+  float* scales_out;          // [M] FP32 row scales, likewise
+  const uint16_t* x;          // [M,K] BF16 activations
 };
 
 // kRowsT: rows of the activation tile in shared memory (16 or 64). kDataRowsT: distinct rows in it
 // (M <= kDataRowsT). <64, 16> is the replicated form: the 16-row box is loaded four times, so every
 // TMEM lane quarter holds a copy of the 16 result rows and eight warps share the epilogue's chunks.
-template <int kSplit, int kRowsT = 16, int kDataRowsT = kRowsT>
+// kDynamicT: the kernel takes BF16 activations and quantizes them itself (row absmax in the prologue,
+// one pack per epilogue-warp lane per stage into the INT8 operand tile); replicated 64-row form only.
+template <int kSplit, int kRowsT = 16, int kDataRowsT = kRowsT, bool kDynamicT = false>
 struct DecodeConfig {
+  static_assert(!kDynamicT || (kRowsT == 64 && kDataRowsT == 16 && kSplit == 1), "dynamic form: replicated tile, no split");
+  static constexpr bool kDynamic = kDynamicT;
+  static constexpr int kXBytes = kDynamicT ? 16 * 128 * 2 : 0;   // BF16 activation tile of a stage (two 64-column boxes)
   static_assert(kRowsT == 16 || kRowsT == 64, "activation tiles of 16 or 64 rows");
   static_assert(kDataRowsT == 16 || (kDataRowsT == 64 && kRowsT == 64), "16 or 64 distinct rows");
   static_assert(kDataRowsT == 16 || kSplit <= 2, "the 64-row reduce buffer only fits for a split of two");
@@ -67,6 +77,7 @@ struct DecodeConfig {
   // kMaxStages): a narrow slab gets more, smaller stages, so the bytes in flight stay the same.
   static constexpr int kRingBytes =
       kRows == 16 ? (kSplit == 1 ? 6 : kSplit == 2 ? 5 : 4) * (kMaxSlab * kBlockK + kABytes)
+      : kDynamicT   ? 5 * (kMaxSlab * kBlockK + kABytes + kXBytes)
       : kReplicated ? (kSplit == 1 ? 5 : kSplit == 2 ? 4 : 3) * (kMaxSlab * kBlockK + kABytes)
                     : (kSplit == 1 ? 5 * (kMaxSlab * kBlockK + kABytes) : 150 * 1024);
   static constexpr int kMaxStages = 24;
@@ -79,17 +90,19 @@ struct DecodeConfig {
   static constexpr int kMmaWarp = kRows == 16 ? 1 : 8;
   static constexpr int kTmaWarp = kRows == 16 ? 2 : 9;
   static constexpr int kThreads = kRows == 16 ? 160 : 320;
-  static constexpr int kBarrierBytes = 512;
-  static constexpr int kScaleBytes = kMaxSlab * 4 + 8 * 16 * 4;   // FP32 channel scales of the slab + row sums per warp
+  static constexpr int kBarrierBytes = 1024;
+  // FP32 channel scales of the slab + row sums per warp + (dynamic form) row scales and their inverses
+  static constexpr int kScaleBytes = kMaxSlab * 4 + 8 * 16 * 4 + 2 * 16 * 4;
   static constexpr int kSmemBytes = kRingBytes + kAOperandPad + kReduceBytes + kBarrierBytes + kScaleBytes + 1024;
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
-template <int kSplit, bool kBiased, int kRows = 16, int kDataRows = kRows>
-__global__ void __launch_bounds__((DecodeConfig<kSplit, kRows, kDataRows>::kThreads), 1)
+template <int kSplit, bool kBiased, int kRows = 16, int kDataRows = kRows, bool kDynamic = false>
+__global__ void __launch_bounds__((DecodeConfig<kSplit, kRows, kDataRows, kDynamic>::kThreads), 1)
 decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
                    const __grid_constant__ CUtensorMap map_a, const DecodeParams p) {
-  using Cfg = DecodeConfig<kSplit, kRows, kDataRows>;
+  static_assert(!(kDynamic && kBiased), "the dynamic form takes signed weights");
+  using Cfg = DecodeConfig<kSplit, kRows, kDataRows, kDynamic>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -102,10 +115,12 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kMaxStages + s); };
   const uint32_t done_bar = bar_base + 8u * (2 * Cfg::kMaxStages);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_region + 8 * (2 * Cfg::kMaxStages + 1));
+  auto ready_bar = [&](int s) { return bar_base + 8u * (2 * Cfg::kMaxStages + 1 + s); };   // dynamic form
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_region + 8 * (3 * Cfg::kMaxStages + 1));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* scale_tab = reinterpret_cast<float*>(bar_region + Cfg::kBarrierBytes);          // [kMaxSlab]
   int32_t* row_sums = reinterpret_cast<int32_t*>(scale_tab + Cfg::kMaxSlab);             // [warp][16]
+  float* row_scales = reinterpret_cast<float*>(row_sums + 8 * 16);                        // [16] scale, [16] inverse
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const uint32_t rank = kSplit > 1 ? cluster_ctarank() : 0u;
@@ -115,13 +130,14 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
   const int kb_begin = static_cast<int>((static_cast<long long>(num_kb) * rank) / kSplit);
   const int kb_end = static_cast<int>((static_cast<long long>(num_kb) * (rank + 1)) / kSplit);
   const int w_bytes = p.slab * Cfg::kBlockK;                 // weight tile of one stage (multiple of 1024)
-  const int stage_bytes = w_bytes + Cfg::kABytes;
+  const int stage_bytes = w_bytes + Cfg::kABytes + Cfg::kXBytes;
   const int num_stages = min(Cfg::kMaxStages, Cfg::kRingBytes / stage_bytes);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < num_stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
+      if constexpr (kDynamic) mbar_init(ready_bar(s), Cfg::kEpilogueWarps);
     }
     mbar_init(done_bar, 1);
     *abort_flag = 0;
@@ -160,12 +176,21 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
         break;
       }
       if (elect_one()) {
-        mbar_arrive_expect_tx(full_bar(stage), tx);
         const uint32_t w_dst = smem_base + stage * stage_bytes;
-        tma_load_2d(w_dst, &map_w, kb * Cfg::kBlockK, n0, full_bar(stage));
+        if constexpr (kDynamic) {
+          // weights and the BF16 activation tile (two 64-column boxes); the INT8 operand tile is written
+          // by the epilogue warps
+          mbar_arrive_expect_tx(full_bar(stage), static_cast<uint32_t>(w_bytes + Cfg::kXBytes));
+          tma_load_2d(w_dst, &map_w, kb * Cfg::kBlockK, n0, full_bar(stage));
+          tma_load_2d(w_dst + w_bytes + Cfg::kABytes, &map_a, kb * Cfg::kBlockK, 0, full_bar(stage));
+          tma_load_2d(w_dst + w_bytes + Cfg::kABytes + Cfg::kXBytes / 2, &map_a, kb * Cfg::kBlockK + 64, 0, full_bar(stage));
+        } else {
+          mbar_arrive_expect_tx(full_bar(stage), tx);
+          tma_load_2d(w_dst, &map_w, kb * Cfg::kBlockK, n0, full_bar(stage));
 #pragma unroll
-        for (int copy = 0; copy < Cfg::kRows / Cfg::kDataRows; ++copy)   // the same box into every lane quarter's rows
-          tma_load_2d(w_dst + w_bytes + copy * Cfg::kDataRows * Cfg::kBlockK, &map_a, kb * Cfg::kBlockK, 0, full_bar(stage));
+          for (int copy = 0; copy < Cfg::kRows / Cfg::kDataRows; ++copy)   // the same box into every lane quarter's rows
+            tma_load_2d(w_dst + w_bytes + copy * Cfg::kDataRows * Cfg::kBlockK, &map_a, kb * Cfg::kBlockK, 0, full_bar(stage));
+        }
       }
       __syncwarp();
       if (++stage == num_stages) { stage = 0; phase ^= 1u; }
@@ -179,7 +204,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     uint32_t phase = 0;
     bool ok = true;
     for (int kb = kb_begin; kb < kb_end; ++kb) {
-      if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(kDynamic ? ready_bar(stage) : full_bar(stage), phase, abort_flag))) { ok = false; break; }
       tcgen05_fence_after();
       const uint32_t w_addr = smem_base + stage * stage_bytes;
       const uint64_t w_desc = smem_desc_sw128(w_addr);
@@ -231,9 +256,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       if (part == 0) my_row_sums[lane >> 1] = sum;
     }
-    // the scales do not depend on the accumulation: fetch them while the weights stream
-    const int chunks = (p.slab + 31) / 32;
-    const float row_scale = (real_row && row < p.m) ? p.sa[row] : 0.f;
+    // the channel scales do not depend on the accumulation: fetch them while the weights stream
 #pragma unroll
     for (int i = 0; i < kMyChunks; ++i) {
       const int c = kChunkStride * i + first_chunk;
@@ -241,6 +264,91 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
       scale_tab[c * 32 + lane] = (c * 32 + lane < p.slab && channel < p.n) ? __bfloat162float(p.sw[channel]) : 0.f;
     }
     __syncwarp();
+    if constexpr (kDynamic) {
+      // ---- row scales: the eight warps scan the BF16 activations once, all 256 threads on one row at a
+      // time with every row's loads issued before the first is used (the scan has to finish while the
+      // ring still has room for the weights streaming in); exactly the row quantizer's absmax -> scale.
+      // Rows past M get scale 1 (their tile rows are zero-filled).
+      const int team = warp * 32 + lane;                 // 0..255
+      float* partial = reinterpret_cast<float*>(row_sums);   // [16][8] warp maxima (the row sums are a biased-form thing)
+      const int packs_in_row = p.k >> 3;
+      // four rows at a time, all of a thread's loads for them in flight together (K <= 8192: at most
+      // four packs per thread and row)
+      constexpr int kScanRows = 4;
+#pragma unroll 1
+      for (int r0 = 0; r0 < 16; r0 += kScanRows) {
+        uint4 v[kScanRows][4];
+#pragma unroll
+        for (int rr = 0; rr < kScanRows; ++rr)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int pk = team + 256 * j;
+            v[rr][j] = (r0 + rr < p.m && pk < packs_in_row)
+                           ? __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(r0 + rr) * p.k) + pk)
+                           : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+        for (int rr = 0; rr < kScanRows; ++rr) {
+          uint32_t packed_max = 0u;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            packed_max = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(packed_max, v[rr][j].x), v[rr][j].y),
+                                                     v[rr][j].z), v[rr][j].w);
+          float maximum = fmaxf(bf16_lo(packed_max), bf16_hi(packed_max));
+#pragma unroll
+          for (int mask = 16; mask; mask >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, mask));
+          if (lane == 0) partial[(r0 + rr) * 8 + warp] = maximum;
+        }
+        if (r0 + kScanRows >= p.m) {   // remaining rows are beyond M: their maxima are zero
+          for (int r = r0 + kScanRows; r < 16; ++r)
+            if (lane == 0) partial[r * 8 + warp] = 0.f;
+          break;
+        }
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight epilogue warps only
+      if (team < 16) {
+        float maximum = partial[team * 8];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) maximum = fmaxf(maximum, partial[team * 8 + i]);
+        const float scale = team < p.m ? fmaxf(__fdiv_rn(maximum, 127.f), 1e-20f) : 1.f;
+        row_scales[team] = scale;
+        row_scales[16 + team] = __fdiv_rn(1.f, scale);
+        if (blockIdx.x == 0 && team < p.m) p.scales_out[team] = scale;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      // ---- per stage: one 16-byte pack of BF16 per lane -> 8 codes into the INT8 operand tile (all
+      // four 16-row slots of it), in the 128-byte-swizzled layout the MMA descriptor expects
+      const int conv_row = team >> 4, pack_in_row = team & 15;
+      const float scale = row_scales[conv_row], inverse = row_scales[16 + conv_row];
+      const int count = kb_end - kb_begin;
+      int kb = count > 0 ? kb_begin + (slab_index * 5) % count : kb_begin;     // the producer's order
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < count; ++i) {
+        if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag))) break;
+        uint8_t* stage_base = smem + stage * stage_bytes + w_bytes;
+        const uint8_t* x_tile = stage_base + Cfg::kABytes;
+        const int box = pack_in_row >> 3, chunk = pack_in_row & 7;
+        const uint4 pack = *reinterpret_cast<const uint4*>(x_tile + box * (Cfg::kXBytes / 2) + conv_row * 128 +
+                                                           ((chunk ^ (conv_row & 7)) << 4));
+        const uint2 codes = quantize_pack(pack, scale, inverse);
+        const int out_chunk = pack_in_row >> 1;          // 16-byte chunk of the 128-byte INT8 row
+        const int offset = conv_row * 128 + ((out_chunk ^ (conv_row & 7)) << 4) + (pack_in_row & 1) * 8;
+#pragma unroll
+        for (int copy = 0; copy < Cfg::kRows / Cfg::kDataRows; ++copy)
+          *reinterpret_cast<uint2*>(stage_base + copy * Cfg::kDataRows * Cfg::kBlockK + offset) = codes;
+        if (blockIdx.x == 0 && conv_row < p.m && kb * Cfg::kBlockK + pack_in_row * 8 < p.k)
+          *reinterpret_cast<uint2*>(p.codes_out + static_cast<size_t>(conv_row) * p.k + kb * Cfg::kBlockK + pack_in_row * 8) = codes;
+        fence_proxy_async_smem();                        // generic-proxy writes -> visible to the MMA's reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready_bar(stage));
+        if (++stage == num_stages) { stage = 0; phase ^= 1u; }
+        if (++kb == kb_end) kb = kb_begin;
+      }
+    }
+    const int chunks = (p.slab + 31) / 32;
+    const float row_scale = kDynamic ? ((real_row && row < p.m) ? row_scales[row] : 0.f)
+                                     : ((real_row && row < p.m) ? p.sa[row] : 0.f);
     const bool have_work = kb_end > kb_begin;
     const bool ok = have_work ? mbar_wait(done_bar, 0u, abort_flag) : true;
     tcgen05_fence_after();

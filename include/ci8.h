@@ -92,6 +92,17 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
                            const void* w_scale, void* out, int m, int n, int groups,
                            ci8_stream_t stream);
 
+/* quantize_rows followed by fused_channel_mm as one call (reference csrc/kernels.cu:283-292 then
+ * csrc/fused_mm.cu:66-93; the reference always launches the two separately). x BF16 [m,k], w INT8
+ * [n,k], w_scale BF16 [n] -> out BF16 [m,n]; codes INT8 [m,k] and scales FP32 [m] receive exactly what
+ * ci8_quantize_rows would write (caller-owned, also usable afterwards). For m <= 16 and k <= 8192, when
+ * the streaming kernel runs unsplit, this is ONE kernel: every CTA derives the row scales from the
+ * activations and quantizes each K block on its way into the MMA operand tile, so the quantizer's
+ * launch disappears from the decode step; otherwise the two kernels are launched back to back. The
+ * results are bit-identical either way. x, codes and w 16-byte aligned; k % 32 == 0. */
+int ci8_dynamic_channel_mm(const void* x, const int8_t* w, const void* w_scale, int8_t* codes,
+                           float* scales, void* out, int m, int n, int k, ci8_stream_t stream);
+
 /* The gate/up projection with the SwiGLU fused into its epilogue. No single counterpart in the
  * reference: it replaces fused_channel_mm (csrc/fused_mm.cu:66-93) followed by silu_mul
  * (csrc/silu_quant.cu:64-88) and produces the same bits as that pair, without writing and re-reading
