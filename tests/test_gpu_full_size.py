@@ -118,3 +118,37 @@ def test_sharded_config_single_gpu_slice(ops):
     want_codes, want_scales = ref.quantize_rows_ref(inputs.x[rows])
     _, want = ref.fused_channel_mm_ref(want_codes, inputs.w, want_scales, inputs.w_scale, fast=True)
     assert_bit_equal(full[rows.to(DEV)], want, "sampled rows")
+
+
+def test_mlp_chain_fused_forms_at_full_size(ops):
+    """The prefill MLP chain through the fused forms, at config 2's sizes: gate_up_silu_mm must equal
+    fused_channel_mm + silu_mul over the whole [4096, 17408] output, and dynamic_channel_mm the
+    quantizer + GEMM pair on the decode shape (a row sample of both is checked against the CPU checker
+    through the unfused operators in test_prefill_configs and test_decode_config)."""
+    from consumer_int8.quantization import interleave_gate_up
+
+    m, n, k = 4096, 34816, 5120
+    inputs = workloads.linear_inputs(m, n, k, seed=3)
+    x, w, sw = inputs.x.to(DEV), inputs.w.to(DEV), (inputs.w_scale.float() * 4).bfloat16().to(DEV)
+    codes, scales = quantize_on_gpu(ops, x)
+    gate_up = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.fused_channel_mm(codes, w, scales, sw, gate_up, 0)
+    want = torch.empty(m, n // 2, dtype=torch.bfloat16, device=DEV)
+    ops.silu_mul(gate_up, want)
+    del gate_up
+    wi, swi = interleave_gate_up(w, sw)
+    got = torch.full((m, n // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gate_up_silu_mm(codes, wi, scales, swi, got)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16)), "fused SwiGLU GEMM differs from the pair"
+    del wi, swi, got, want
+
+    rows = 16
+    out_pair = torch.empty(rows, n, dtype=torch.bfloat16, device=DEV)
+    ops.fused_channel_mm(codes[:rows], w, scales[:rows], sw, out_pair, 0)
+    codes2 = torch.empty(rows, k, dtype=torch.int8, device=DEV)
+    scales2 = torch.empty(rows, device=DEV)
+    out_dynamic = torch.full((rows, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.dynamic_channel_mm(x[:rows], w, sw, codes2, scales2, out_dynamic)
+    assert torch.equal(codes2, codes[:rows]) and torch.equal(scales2, scales[:rows])
+    assert torch.equal(out_dynamic.view(torch.int16), out_pair.view(torch.int16)), "dynamic linear differs from the pair"
+    assert device_status(ops) == 0
