@@ -220,6 +220,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     int stage = 0;
     uint32_t phase = 0;
     const uint32_t leader_full0 = kCtas == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
+    // the raster keeps a group of A rows in L2 while the weights stream past: A lines leave L2 last
+    const uint64_t a_policy = l2_policy_evict_last();
     bool ok = true;
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
       int mt, nt, n_off, n_width;
@@ -240,10 +242,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint32_t bar = leader_full0 + 8u * stage;
             const int kx = kb * Cfg::kBlockK;
             if constexpr (kCtas == 2) {
-              tma_load_2d_pair(a_dst, &map_a, kx, g * p.m + a_row, bar);
+              tma_load_2d_pair_hint(a_dst, &map_a, kx, g * p.m + a_row, bar, a_policy);
               tma_load_2d_pair(b_dst, w_map, g * p.k + kx, w_row, bar);
             } else {
-              tma_load_2d(a_dst, &map_a, kx, g * p.m + a_row, bar);
+              tma_load_2d_hint(a_dst, &map_a, kx, g * p.m + a_row, bar, a_policy);
               tma_load_2d(b_dst, w_map, g * p.k + kx, w_row, bar);
             }
           }
@@ -317,6 +319,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     uint8_t* my_staging = staging + epi * Cfg::kStoreBufs * Cfg::kStoreBoxBytes;
     uint32_t acc_iter = 0, store_iter = 0;
     bool ok = true;
+    const uint64_t store_policy = l2_policy_evict_first();
     float total[kMode == kModeGrouped ? Cfg::kColsPerEpiWarp : 1];
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
       int mt, nt, n_off, n_width;
@@ -392,7 +395,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
               fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0 && row0 < p.m) {
-                tma_store_2d(&out_maps.map[0], smem_u32(box), c0, row0);
+                tma_store_2d_hint(&out_maps.map[0], smem_u32(box), c0, row0, store_policy);
                 tma_store_commit();
               }
               ++store_iter;

@@ -133,6 +133,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* map, int x
       "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// The two loads with an L2 eviction-priority hint.
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const void* map, int x, int y, uint32_t bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair_hint(uint32_t dst, const void* map, int x, int y, uint32_t bar,
+                                                      uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar), "l"(policy)
+      : "memory");
+}
 // Same load issued from a CTA of a 2-CTA pair; `bar` is a shared::cluster address and may
 // name the pair leader's mbarrier (the data still lands in the issuing CTA's shared memory).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* map, int x, int y,
@@ -151,6 +168,26 @@ __device__ __forceinline__ void tma_store_2d(const void* map, uint32_t src, int 
                    reinterpret_cast<uint64_t>(map)),
                "r"(src), "r"(x), "r"(y)
                : "memory");
+}
+// The same store with an L2 eviction-priority hint (a policy from l2_policy_evict_first()).
+__device__ __forceinline__ void tma_store_2d_hint(const void* map, uint32_t src, int x, int y, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(x), "r"(y), "l"(policy)
+               : "memory");
+}
+// Lines written or read under this policy are the first to leave L2: for data that is touched once
+// (a GEMM's output) so that it does not push out operands that are about to be reused.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+// Lines read under this policy are the last to leave L2: for the operand that the raster keeps reusing.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
 }
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
