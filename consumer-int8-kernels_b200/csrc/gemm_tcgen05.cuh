@@ -500,7 +500,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0 && row0 < p.m) {
-              for (int d = 0; d < p.num_outputs; ++d)
+              // destination 0 is this GPU's own memory: written once, so it should not displace the A
+              // rows and W tiles that the next tiles read again; the others are peers' buffers
+              tma_store_2d_hint(&out_maps.map[0], smem_u32(box), c0, row0, store_policy);
+              for (int d = 1; d < p.num_outputs; ++d)
                 tma_store_2d(&out_maps.map[d], smem_u32(box), c0, row0);
               tma_store_commit();
             }
