@@ -40,6 +40,7 @@ WORKLOADS = {
     "prefill_down": dict(m=4096, k=17408, n=5120, config="configs[2]"),
     "grouped": dict(m=2048, k=32768, n=7168, groups=8, config="configs[3]"),
     "decode": dict(m=16, k=5120, n=34816, config="configs[1]"),
+    "q8_block": dict(m=4096, k=4096, n=1024, config="block-32 Q8_0 (the reference's benchmark shape)"),
 }
 METRIC = "W8A8 GEMM INT8 TOPS (quantize_rows + fused_channel_mm, whole job)"
 
@@ -507,7 +508,20 @@ def profile_only(args, spec):
 
     device = torch.device("cuda", 0)
     m, n, k = spec["m"], spec["n"], spec["k"]
-    if args.workload == "grouped":
+    if args.workload == "q8_block":
+        import ctypes
+        gen = torch.Generator().manual_seed(0)
+        w = torch.randint(-128, 128, (n, k), dtype=torch.int8, generator=gen).to(device)
+        sw = (torch.randn(n, k // 32, generator=gen) * 0.01).half().to(device)
+        x = (torch.randn(m, k, generator=gen) * 0.1).bfloat16().to(device)
+        a = torch.empty(m, k, dtype=torch.int8, device=device)
+        sa = torch.empty(m, k // 32, device=device)
+        y = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for _ in range(args.steps):
+            rc = ops.libci8.ci8_q8_block_mm(*(ctypes.c_void_p(t.data_ptr()) for t in (x, a, sa, w, sw, y)), m, n, k, stream)
+            assert rc == 0, rc
+    elif args.workload == "grouped":
         inputs = workloads.grouped_inputs(m, n, spec["groups"], seed=0)
         x, w, sw = inputs.x.to(device), inputs.w.to(device), inputs.w_scale.to(device)
         codes = torch.empty(spec["groups"], m, 4096, dtype=torch.int8, device=device)
@@ -528,6 +542,7 @@ def profile_only(args, spec):
             ops.fused_channel_mm(codes, copies[i % len(copies)], scales, sw, out, args.schedule)
             if args.workload == "decode":
                 ops.channel_gemv(x, copies[i % len(copies)], sw, out)
+                ops.dynamic_channel_mm(x, copies[i % len(copies)], sw, codes, scales, out)
     torch.cuda.synchronize()
     print(json.dumps(dict(profile_only=args.workload, launches=args.steps)), flush=True)
 
@@ -558,8 +573,8 @@ def main():
     if args.profile_only:
         profile_only(args, spec)
         return
-    if args.workload in ("decode", "grouped"):
-        raise SystemExit("the decode and grouped workloads are timed inside the default run (other_configs) "
+    if args.workload in ("decode", "grouped", "q8_block"):
+        raise SystemExit("the decode, grouped and q8_block workloads are timed inside the default run (other_configs) "
                          "or launched with --profile-only")
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
