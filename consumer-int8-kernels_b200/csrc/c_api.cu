@@ -509,6 +509,37 @@ cudaError_t launch_q8_block(const void* x, int8_t* a, float* sa, const int8_t* w
                            Cfg::kSmemBytes, stream, map_a, map_w, p);
 }
 
+// ------------------------------------------------------------------ block-32 with built-in scratch
+// Scratch of ci8_q8_block_mm_static: the activation codes (one byte per value) followed, at a fixed
+// offset, by their FP32 block scales (one per 32 values). It is part of the library image, so every
+// GPU that loads libci8.so carries these 4.5 MiB until the process exits.
+constexpr long long kQ8StaticMaxValues = 4ll << 20;                      // m * k of one call
+constexpr long long kQ8StaticScaleOffset = kQ8StaticMaxValues;           // bytes; a multiple of 256
+constexpr long long kQ8StaticBytes = kQ8StaticMaxValues + kQ8StaticMaxValues / 32 * 4;
+static __device__ __align__(256) unsigned char g_q8_static_scratch[kQ8StaticBytes];
+
+// Device address of the scratch on the current device. In host code `g_q8_static_scratch` is only a
+// handle for the runtime, not an address a kernel (or a tensor map) could use, so the address is asked
+// for once per device, with that device current, and remembered.
+cudaError_t q8_static_scratch(unsigned char** out) {
+  static std::atomic<unsigned char*> cached[kMaxDevices];
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return err;
+  if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  unsigned char* address = cached[device].load(std::memory_order_acquire);
+  if (!address) {
+    void* looked_up = nullptr;
+    err = cudaGetSymbolAddress(&looked_up, g_q8_static_scratch);
+    if (err != cudaSuccess) return err;
+    if (!looked_up) return cudaErrorInvalidSymbol;
+    address = static_cast<unsigned char*>(looked_up);
+    cached[device].store(address, std::memory_order_release);
+  }
+  *out = address;
+  return cudaSuccess;
+}
+
 // ====================================================================== C ABI
 extern "C" {
 
@@ -756,6 +787,24 @@ int ci8_q8_block_mm(const void* x, int8_t* a, float* sa, const int8_t* w, const 
     return kInvalid;
   return launch_q8_block(x, a, sa, w, sw, y, m, n, k, reinterpret_cast<cudaStream_t>(stream));
 }
+
+int ci8_q8_block_mm_static(const void* x, const int8_t* w, const void* sw, void* y, int m, int n, int k,
+                           ci8_stream_t stream) {
+  if (!x || !w || !sw || !y || m <= 0 || n <= 0 || k <= 0 || k % 32 != 0 || k > 65536 ||
+      static_cast<long long>(n) * k > INT32_MAX || static_cast<long long>(m) * n > INT32_MAX || !aligned(x, 16) ||
+      !aligned(w, 16) || !aligned(sw, 2))
+    return kInvalid;
+  if (static_cast<long long>(m) * k > kQ8StaticMaxValues) return kInvalid;   // does not fit the built-in scratch
+  unsigned char* scratch = nullptr;
+  const cudaError_t err = q8_static_scratch(&scratch);
+  if (err != cudaSuccess) return err;
+  // every code and scale the product kernel reads is written by the quantizer of the same call first
+  // (rows past m are zero-filled by the tensor map), so nothing left over from an earlier call is seen
+  return launch_q8_block(x, reinterpret_cast<int8_t*>(scratch), reinterpret_cast<float*>(scratch + kQ8StaticScaleOffset),
+                         w, sw, y, m, n, k, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ci8_q8_block_static_max_values(void) { return static_cast<int>(kQ8StaticMaxValues); }
 
 // Test hook: the streaming kernel with a forced split-K factor (1, 2 or 4; at most 2 above 16 rows);
 // weights_biased != 0 selects the UINT8 form. Same contract as ci8_fused_channel_mm / ci8_channel_mm.

@@ -124,6 +124,27 @@ int ci8_gate_up_silu_mm(const int8_t* a, const int8_t* w, const float* a_scale, 
 int ci8_q8_block_mm(const void* x, int8_t* a, float* sa, const int8_t* w, const void* sw, void* y,
                     int m, int n, int k, ci8_stream_t stream);
 
+/* ci8_q8_block_mm for callers that have no device memory to hand over. It has no counterpart in the
+ * reference. ci8_q8_block_mm needs two caller-owned scratch buffers (the activation codes and their
+ * block scales); some callers cannot provide them: a plugin that runs inside a serving engine whose
+ * memory pool already owns the whole GPU (a cudaMalloc there fails or fragments the pool), code that
+ * runs while a stream is being captured (allocation is not allowed then), or a host that simply has no
+ * allocator wired up. This variant keeps that scratch inside the library instead: a fixed array in
+ * device memory (4.5 MiB, present on every GPU that loads the library until the process exits). It
+ * calls no cudaMalloc / cudaFree and no allocating library routine. Inputs x, w, sw and the output y
+ * are as for ci8_q8_block_mm and still belong to the caller.
+ *   Limit: m * k <= ci8_q8_block_static_max_values() (4 Mi values, e.g. 1024 rows of K = 4096);
+ *   anything larger is rejected with cudaErrorInvalidValue before any launch.
+ *   First use: the first call on each device looks up the array's device address (with that device
+ *   current); make that call once before capturing a stream.
+ *   Sharing: every call on a device uses the same array. Calls are safe back to back on one stream;
+ *   calls that may run at the same time on the GPU (two streams, two host threads) overwrite each
+ *   other's codes and give wrong results. Nothing has to be cleared between calls: each call writes
+ *   every code and scale it later reads. The array's contents after a call are unspecified. */
+int ci8_q8_block_mm_static(const void* x, const int8_t* w, const void* sw, void* y, int m, int n, int k,
+                           ci8_stream_t stream);
+int ci8_q8_block_static_max_values(void);
+
 /* fused_channel_mm for an output-channel shard, with the all-gather of the result fused into the
  * GEMM's epilogue. The reference has no collective (its serving stack gathers column-parallel
  * results outside the library, benchmarks/microbench.py:187); this entry point replaces
