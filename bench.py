@@ -14,8 +14,12 @@ GPU, the all-gather of the BF16 output). Workloads (shapes of the five benchmark
 ``value`` is whole-job throughput with inputs resident in HBM; ``e2e`` is the same metric through
 the public operators with host buffers (pinned host -> device copy of the activations and
 device -> host copy of the result inside the timed region). ``--impl reference`` times the
-reference's own host restatement of the path (torch on the CPU) on a bounded row sample.
-Inputs are synthetic (no dataset stands behind this path) and larger than L2.
+reference's own host restatement of the path (torch on the CPU), on the whole workload when that
+fits the time budget and on a bounded row sample otherwise.
+Before anything is timed, a seeded sample of rows of the result on EVERY rank is compared bit for bit
+with the CPU checker (the reference's discipline: benchmarks/microbench.py:206-214 asserts equality
+before it times); a mismatch ends the run with a non-zero exit code, and the line carries
+``"parity": true``. Inputs are synthetic (no dataset stands behind this path) and larger than L2.
 """
 from __future__ import annotations
 
@@ -132,7 +136,8 @@ def cpu_sample(spec, target_seconds: float = 12.0):
     t0 = time.perf_counter()
     cpu_path(x, w_t, w_scale)
     per_row = (time.perf_counter() - t0) / probe
-    rows = int(max(32, min(spec["m"], target_seconds / 3 / max(per_row, 1e-9))))
+    # the whole workload when three passes fit into about half a minute, else a bounded row sample
+    rows = spec["m"] if per_row * spec["m"] * 3 <= 30.0 else int(max(32, min(spec["m"], target_seconds / 3 / max(per_row, 1e-9))))
     rows -= rows % 8
     x = workloads.activations(rows, k, gen)
     best = min(_timed(lambda: cpu_path(x, w_t, w_scale)) for _ in range(3))
@@ -164,8 +169,13 @@ def run_reference(args, spec, rank):
     cpu_path(probe, w_t, w_scale)
     per_row = _timed(lambda: cpu_path(probe, w_t, w_scale)) / 32
     warmup = max(args.warmup, 1)
-    rows = int(90.0 / (args.steps + warmup) / max(per_row, 1e-9))
-    rows = max(24, min(spec["m"], rows - rows % 8))
+    # every step is the whole workload when warm-up plus K steps then end within about four minutes
+    # (so that both arms run the same configuration), else a row sample sized for a minute and a half
+    if per_row * spec["m"] * (args.steps + warmup) <= 240.0:
+        rows = spec["m"]
+    else:
+        rows = int(90.0 / (args.steps + warmup) / max(per_row, 1e-9))
+        rows = max(24, min(spec["m"], rows - rows % 8))
     x = workloads.activations(rows, k, gen)
     for _ in range(warmup):
         cpu_path(x, w_t, w_scale)
@@ -181,13 +191,43 @@ def run_reference(args, spec, rank):
                 ms_per_step=seconds * 1e3, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="int8",
                 data="synthetic", impl="reference",
                 config=dict(workload=f"{args.workload} {spec['config']} M={spec['m']} K={k} N={n}",
-                            step=f"{rows}-row sample per step on the host CPU"),
+                            step=("the whole workload per step on the host CPU" if rows == spec["m"] else
+                                  f"{rows}-row sample per step on the host CPU")),
                 cpu_baseline=sample, e2e=dict(value=tops, unit="TOPS", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line), flush=True)
 
 
 # ----------------------------------------------------------------------------- GPU arm
+NVLINK_PEER_GBS = 770.0      # measured peer copy on this pool, per direction per GPU (nominal 900)
+
+
+def check_parity(plan, gathered, x_host, w, w_scale, device, rows_checked=32):
+    """A seeded sample of rows of the whole [M, N] result on this rank against the CPU checker."""
+    from oracle import w8a8_ref as ref
+
+    rows = torch.randperm(plan.m, generator=torch.Generator().manual_seed(1234))[:rows_checked].sort().values
+    codes, scales = ref.quantize_rows_ref(x_host[rows])
+    _, want = ref.fused_channel_mm_ref(codes, w, scales, w_scale, fast=True)
+    chunk, local = rows // plan.chunk_m, rows % plan.chunk_m
+    got = gathered[chunk.to(device), :, local.to(device)]            # [rows, G, N/G]
+    got = got.reshape(len(rows), plan.n).cpu()
+    return bool(torch.equal(got.view(torch.int16), want.view(torch.int16)))
+
+
+def source_tag() -> str:
+    """Short hash of the GEMM kernel's source: DRAM-traffic figures from an ncu capture are only
+    current while this matches the tag recorded with them."""
+    import hashlib
+
+    digest = hashlib.sha256()
+    for name in ("gemm_tcgen05.cuh", "sm100_ptx.cuh"):
+        digest.update((ROOT / "consumer-int8-kernels_b200" / "csrc" / name).read_bytes())
+    return digest.hexdigest()[:12]
+
+
 def run_ours(args, spec, rank, world, local_rank):
+    import ctypes
+
     import torch.distributed as dist
     from consumer_int8 import ops, workloads
     from consumer_int8.sharded import ColumnShardedLinear, ShardPlan
@@ -198,12 +238,11 @@ def run_ours(args, spec, rank, world, local_rank):
     gen = torch.Generator().manual_seed(0)
     x_host = workloads.activations(m, k, gen).pin_memory()
     w, w_scale = workloads.weights(n, k, gen)
-    fused = args.gather == "fused" and world > 1
-    plan = ShardPlan(m, n, k, world, rank, chunks=args.chunks if world > 1 and not fused else 1)
+    mode = args.gather if world > 1 else "nccl"
+    fused = mode in ("fused", "fused_nccl_barrier")
+    plan = ShardPlan(m, n, k, world, rank, chunks=args.chunks if mode == "nccl" and world > 1 else 1)
     w_shard, sw_shard = plan.shard_weights(w, w_scale)
-    del w
-    layer = ColumnShardedLinear(plan, w_shard.to(device), sw_shard.to(device), schedule=args.schedule,
-                                mode="fused" if fused else "nccl")
+    layer = ColumnShardedLinear(plan, w_shard.to(device), sw_shard.to(device), schedule=args.schedule, mode=mode)
     x = x_host.to(device)
     out_host = torch.empty(m, plan.shard_n, dtype=torch.bfloat16).pin_memory()
 
@@ -213,7 +252,21 @@ def run_ours(args, spec, rank, world, local_rank):
         torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
-        layer.forward(x)
+        gathered = layer.forward(x)
+    barrier()
+
+    # ---- parity gate: nothing is timed before every rank's result has been checked
+    ok = check_parity(plan, gathered, x_host, w, w_scale, device)
+    if fused:     # the other buffer set as well
+        ok = check_parity(plan, layer.forward(x), x_host, w, w_scale, device) and ok
+    del w
+    verdict = torch.tensor([1 if ok else 0], device=device)
+    if world > 1:
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+    if verdict.item() != 1:
+        print(f"bench: rank {rank}: the result differs from the CPU checker ({'this rank' if not ok else 'another rank'}); "
+              "nothing was timed", file=sys.stderr, flush=True)
+        raise SystemExit(3)
     barrier()
 
     # ---- device-resident timed region (K steps), GEMM timed per launch on the same stream
@@ -236,28 +289,34 @@ def run_ours(args, spec, rank, world, local_rank):
         barrier()
     step_ms = starts[0].elapsed_time(end) / args.steps
     gemm_ms = statistics.mean(a.elapsed_time(b) for a, b in zip(gemm0, gemm1)) if world == 1 else None
+    sharded_ms = None
     if world > 1:
-        # GEMM-only time of this rank's shard, measured in a separate short loop
+        # GEMM-only time of this rank's shard, and the step without any gather (the result stays
+        # column-sharded, [M, N/G] per rank), each in a separate short loop
         barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         a.record()
         for _ in range(10):
-            for c in range(plan.chunks):
-                rows = slice(c * plan.chunk_m, (c + 1) * plan.chunk_m)
-                ops.fused_channel_mm(layer.codes[rows], layer.w, layer.scales[rows], layer.w_scale, layer.local_block(c), args.schedule)
+            for ch in range(plan.chunks):
+                rows = slice(ch * plan.chunk_m, (ch + 1) * plan.chunk_m)
+                ops.fused_channel_mm(layer.codes[rows], layer.w, layer.scales[rows], layer.w_scale, layer.local_block(ch), args.schedule)
         b.record()
+        for _ in range(10):
+            ops.quantize_rows(x, layer.codes, layer.scales)
+            ops.fused_channel_mm(layer.codes, layer.w, layer.scales, layer.w_scale, layer.gathered.view(world, m, plan.shard_n)[rank], args.schedule)
+        c.record()
         barrier()
-        gemm_ms = a.elapsed_time(b) / 10
-        t = torch.tensor([step_ms, gemm_ms], device=device)
+        gemm_ms, sharded_ms = a.elapsed_time(b) / 10, b.elapsed_time(c) / 10
+        t = torch.tensor([step_ms, gemm_ms, sharded_ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        step_ms, gemm_ms = t.tolist()
+        step_ms, gemm_ms, sharded_ms = t.tolist()
 
     # ---- end-to-end region: host activations in, this rank's output block out, every step.
     # Two sets of device buffers and two copy streams: the device->host copy of step i runs while
     # step i+1's host->device copy and kernels run (both directions of the link in use at once).
+    # The fused layer alternates its own two result buffers; the other modes get a second layer.
     e2e_steps = max(4, min(args.steps, 12))
-    layers = [layer, ColumnShardedLinear(plan, layer.w, layer.w_scale, schedule=args.schedule,
-                                         mode="fused" if fused else "nccl")]
+    layers = [layer, layer if fused else ColumnShardedLinear(plan, layer.w, layer.w_scale, schedule=args.schedule, mode=mode)]
     xs = [x, torch.empty_like(x)]
     outs_host = [out_host, torch.empty_like(out_host).pin_memory()]
     main = torch.cuda.current_stream()
@@ -266,7 +325,7 @@ def run_ours(args, spec, rank, world, local_rank):
     compute_done = [torch.cuda.Event() for _ in range(2)]
     out_done = [torch.cuda.Event() for _ in range(2)]
     for _ in range(2):
-        layers[1].forward(xs[0])        # warm the second set (and its symmetric-memory mapping)
+        layers[1].forward(xs[0])        # warm the second set
     barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
@@ -277,13 +336,13 @@ def run_ours(args, spec, rank, world, local_rank):
             xs[s].copy_(x_host, non_blocking=True)
             in_done[s].record()
         main.wait_event(in_done[s])
-        main.wait_event(out_done[s])                     # step i-2's result has left layers[s].gathered
+        main.wait_event(out_done[s])                     # step i-2's result has left its buffer
         gathered = layers[s].forward(xs[s])
         compute_done[s].record()
         with torch.cuda.stream(copy_out):
             copy_out.wait_event(compute_done[s])
-            for c in range(plan.chunks):
-                outs_host[s][c * plan.chunk_m:(c + 1) * plan.chunk_m].copy_(gathered[c, rank], non_blocking=True)
+            for ch in range(plan.chunks):
+                outs_host[s][ch * plan.chunk_m:(ch + 1) * plan.chunk_m].copy_(gathered[ch, rank], non_blocking=True)
             out_done[s].record()
     main.wait_stream(copy_out)
     b.record()
@@ -294,35 +353,59 @@ def run_ours(args, spec, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = t.item()
 
-    status = ops.libci8.ci8_device_status
-    import ctypes
     word = ctypes.c_uint(0)
-    status(ctypes.byref(word))
+    ops.libci8.ci8_device_status(ctypes.byref(word))
     if rank != 0:
         return
     peaks, peak_kind = measured_peaks()
     ops_total = 2.0 * m * n * k
-    tensor_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    # INT8 issues at twice the BF16 rate: the peak is 2 x the measured BF16 figure, the burst one for a
+    # timed region shorter than a second, the sustained one for a longer loop
+    region_s = step_ms * args.steps / 1e3
+    burst_peak, sustained_peak = 2.0 * peaks["bf16_tflops"], 2.0 * peaks["bf16_tflops_sustained"]
+    tensor_peak = burst_peak if region_s < 1.0 else sustained_peak
     gemm_tops = 2.0 * m * plan.shard_n * k / (gemm_ms * 1e-3) / 1e12
+    traffic = KERNEL_TRAFFIC.get(args.workload if world == 1 else f"{args.workload}/{world}")
+    algorithmic = float(m * k + plan.shard_n * k + 2 * m * plan.shard_n + 4 * m + 2 * plan.shard_n)
+    roofline = dict(bound="tensor", achieved=gemm_tops, peak=tensor_peak, unit="TFLOP/s", frac=gemm_tops / tensor_peak,
+                    frac_sustained=gemm_tops / sustained_peak, frac_nominal=gemm_tops / 4500.0,
+                    traffic=traffic["read"] + traffic["write"] if traffic else None,
+                    traffic_ratio=(traffic["read"] + traffic["write"]) / algorithmic if traffic else None,
+                    traffic_source=traffic["source"] if traffic else None, kernel_source=source_tag(),
+                    kernel="gemm_i8_kernel<2,fused>",
+                    note=f"integer ops 2*M*N*K per launch / CUDA-event launch time ({gemm_ms:.3f} ms, per GPU); peak = 2 x "
+                         f"{'bf16_tflops (burst' if region_s < 1.0 else 'bf16_tflops_sustained (long'} region, {region_s:.2f} s) of "
+                         f"{peak_kind}; traffic is current when traffic_source equals kernel_source")
     line = dict(
         metric=METRIC, value=ops_total / (step_ms * 1e-3) / 1e12, unit="TOPS", n_gpus=world, steps=args.steps,
         warmup=max(args.warmup, 3), ms_per_step=step_ms, higher_is_better=True, scaling="strong", vs_baseline=None,
-        dtype="int8", data="synthetic",
+        dtype="int8", data="synthetic", parity=True,
         config=dict(workload=f"{args.workload} {spec['config']} M={m} K={k} N={n}", parallelism=f"N-sharded x{world}",
                     gather=("none" if world == 1 else
-                            "fused: GEMM epilogue TMA-stores each tile into every rank's symmetric-memory buffer" if fused
-                            else "NCCL all-gather of BF16 [M,N/G] blocks"),
+                            "fused: GEMM epilogue TMA-stores each tile into every rank's symmetric-memory buffer, closed by "
+                            "an in-kernel rendezvous" if mode == "fused" else
+                            "fused stores closed by an NCCL barrier" if mode == "fused_nccl_barrier" else
+                            "NCCL all-gather of BF16 [M,N/G] blocks"),
                     row_chunks=plan.chunks, schedule=args.schedule,
+                    parity="32 seeded rows of the whole result on every rank, bit for bit against the CPU checker, before timing",
                     l2="inputs larger than L2 (weights+activations+output per step exceed 126 MB); no flush"),
-        roofline=dict(bound="tensor", achieved=gemm_tops, peak=tensor_peak, unit="TFLOP/s", frac=gemm_tops / tensor_peak,
-                      traffic=KERNEL_TRAFFIC.get(args.workload) if world == 1 else None, kernel="gemm_i8_kernel<2,fused>",
-                      note=f"integer ops 2*M*N*K per launch / CUDA-event launch time ({gemm_ms:.3f} ms, per GPU); peak = 2 x "
-                           f"bf16_tflops_sustained of {peak_kind} (INT8 issues at twice the BF16 rate); "
-                           f"vs nominal 4500 dense INT8: {gemm_tops / 4500:.3f}"),
+        roofline=roofline,
         e2e=dict(value=ops_total / (e2e_ms * 1e-3) / 1e12, unit="TOPS", h2d_bytes_per_step=x_host.numel() * 2,
-                 d2h_bytes_per_step=out_host.numel() * 2, ms_per_step=e2e_ms, steps=e2e_steps),
+                 d2h_bytes_per_step=out_host.numel() * 2, ms_per_step=e2e_ms, steps=e2e_steps,
+                 note="per rank: the activations in, this rank's [M, N/G] block out (the whole result reaches the host once)"),
         gpu_launches=args.steps * (1 + plan.chunks), clocks=clocks.summary(), device_status=word.value,
     )
+    if world > 1:
+        bytes_in = plan.gather_bytes_received
+        floor_ms = bytes_in / NVLINK_PEER_GBS / 1e6
+        line["gather"] = dict(bytes_in_per_gpu=bytes_in, achieved_gbs=bytes_in / step_ms / 1e6, floor_ms=floor_ms,
+                              floor_ms_nominal_900=bytes_in / 900.0 / 1e6, frac=floor_ms / step_ms,
+                              gemm_only_ms=gemm_ms,
+                              note=f"every GPU must receive (G-1)/G of the BF16 result; floor = bytes / {NVLINK_PEER_GBS:.0f} GB/s "
+                                   "(measured peer copy per direction); achieved over the whole step")
+        line["column_sharded"] = dict(ms_per_step=sharded_ms, value=ops_total / (sharded_ms * 1e-3) / 1e12, unit="TOPS",
+                                      note="the same step without the gather: the result stays [M, N/G] per rank "
+                                           "(ColumnShardedLinear mode='none'), what a row-parallel consumer takes")
     if world == 1:
         sample, _, _ = cpu_sample(spec)
         line["cpu_baseline"] = sample
@@ -331,17 +414,26 @@ def run_ours(args, spec, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
-# DRAM bytes (read + write) per launch of the dominant kernel from the ncu captures summarised
-# under profiles/ (null until a capture of that workload exists).
+# DRAM bytes per launch of the dominant kernel from ncu captures (dram__bytes_read.sum and
+# dram__bytes_write.sum) summarised under profiles/, each tagged with source_tag() of the kernel
+# source it was taken from: a figure whose tag differs from the running kernel's is stale.
 KERNEL_TRAFFIC = {
-    # gemm_i8_kernel<2,fused>: dram__bytes_read.sum + dram__bytes_write.sum per launch
-    "sharded": 715.9e6 + 1111.1e6,          # profiles/gemm_i8_kernel_sharded_traffic.md (algorithmic: 1403 MB)
-    "prefill_gate_up": 202.4e6 + 255.5e6,   # profiles/gemm_i8_kernel_prefill_gate_up.md (algorithmic: 484.5 MB)
-    "prefill_down": 455.0e6 + 37.5e6,       # profiles/gemm_i8_kernel_prefill_down.md (algorithmic: 212.8 MB)
+    "sharded": dict(read=715.9e6, write=1111.1e6, source="round-1 kernel", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
+    "prefill_gate_up": dict(read=202.4e6, write=255.5e6, source="round-1 kernel", profile="profiles/gemm_i8_kernel_prefill_gate_up.md"),
+    "prefill_down": dict(read=455.0e6, write=37.5e6, source="round-1 kernel", profile="profiles/gemm_i8_kernel_prefill_down.md"),
 }
 
 
-def _time_graph(fn, launches, replays=5):
+class Timing(float):
+    """Median milliseconds per launch, with the fastest and slowest replay attached."""
+
+    lo: float
+    hi: float
+
+
+def _time_graph(fn, launches, replays=7):
+    """The reference's method (benchmarks/microbench.py:15-38): warm up, capture `launches` calls in
+    one CUDA graph, replay it seven times, report the median (with min and max)."""
     for _ in range(3):
         fn(0)
     torch.cuda.synchronize()
@@ -357,7 +449,13 @@ def _time_graph(fn, launches, replays=5):
         b.record()
         b.synchronize()
         times.append(a.elapsed_time(b) / launches)
-    return statistics.median(times)
+    result = Timing(statistics.median(times))
+    result.lo, result.hi = min(times), max(times)
+    return result
+
+
+def _spread_us(t):
+    return [t.lo * 1e3, t.hi * 1e3]
 
 
 def other_configs(ops, workloads, device, peaks):
@@ -365,7 +463,7 @@ def other_configs(ops, workloads, device, peaks):
     rotating input copies larger than L2 (the reference's method, benchmarks/microbench.py:15-38)."""
     results = {}
     hbm = peaks["hbm_gbs"]
-    tensor_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    tensor_peak = 2.0 * peaks["bf16_tflops"]      # each graph replay lasts milliseconds: the burst figure applies
     gen = torch.Generator().manual_seed(0)
     # decode: rotate four weight copies (4 x 178 MB) so every launch streams from HBM
     n, k = 34816, 5120
@@ -390,12 +488,14 @@ def other_configs(ops, workloads, device, peaks):
         # BF16 activations in, one kernel: the quantizer runs inside the streaming kernel
         ms_dyn = _time_graph(lambda i: ops.dynamic_channel_mm(x, copies[i % 4], sw, codes, scales, out), 40)
         dyn_bytes = n * k + 2 * n + 2 * m * k + 2 * m * n
-        results[f"decode_m{m}"] = dict(us=ms * 1e3, gbs=nbytes / ms / 1e6, frac_hbm=nbytes / ms / 1e6 / hbm,
+        results[f"decode_m{m}"] = dict(us=ms * 1e3, us_min_max=_spread_us(ms), gbs=nbytes / ms / 1e6, frac_hbm=nbytes / ms / 1e6 / hbm,
+                                       frac_nominal_8000=nbytes / ms / 1e6 / 8000.0,
                                        channel_mm_u8_us=ms_u8 * 1e3, with_quantize_us=ms_q * 1e3,
                                        dynamic_us=ms_dyn * 1e3, dynamic_gbs=dyn_bytes / ms_dyn / 1e6,
                                        dynamic_frac_hbm=dyn_bytes / ms_dyn / 1e6 / hbm,
                                        channel_gemv_us=ms_gemv * 1e3,
-                                       channel_gemv_gbs=(n * k + 2 * n + 2 * m * k + 2 * m * n) / ms_gemv / 1e6)
+                                       channel_gemv_gbs=(n * k + 2 * n + 2 * m * k + 2 * m * n) / ms_gemv / 1e6,
+                                       channel_gemv_frac_hbm=(n * k + 2 * n + 2 * m * k + 2 * m * n) / ms_gemv / 1e6 / hbm)
     # rows between decode and a full tile: the streaming kernel up to 64 rows, the 128-row GEMM tile beyond
     for m in (32, 64, 128):
         x = workloads.activations(m, k, gen).to(device)
@@ -433,11 +533,26 @@ def other_configs(ops, workloads, device, peaks):
         out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
         ops.quantize_rows(x, codes, scales)
         ms = _time_graph(lambda i: ops.fused_channel_mm(codes, wd, scales, sw, out, 0), 20)
+        # the same product from UINT8 code+128 weights (channel_mm) and with the INT32 accumulators
+        # written out as well (cutlass_channel_mm)
+        wu8 = (w.to(torch.int16) + 128).to(torch.uint8).to(device)
+        ms_u8 = _time_graph(lambda i: ops.channel_mm(codes, wu8, scales, sw, out), 20)
+        del wu8
+        workspace = torch.empty(m, n, dtype=torch.int32, device=device)
+        ms_ws = _time_graph(lambda i: ops.cutlass_channel_mm(codes, wd, scales, sw, workspace, out), 10)
+        del workspace
         xs = [x.clone() for _ in range(4)]
         ms_q = _time_graph(lambda i: ops.quantize_rows(xs[i % 4], codes, scales), 40)
         tops = 2.0 * m * n * k / ms / 1e9
-        results[name] = dict(gemm_ms=ms, tops=tops, frac_tensor=tops / tensor_peak, frac_nominal_4500=tops / 4500,
-                             quantize_us=ms_q * 1e3, quantize_gbs=(3 * m * k + 4 * m) / ms_q / 1e6)
+        results[name] = dict(gemm_ms=ms, gemm_ms_min_max=[ms.lo, ms.hi], tops=tops, frac_tensor=tops / tensor_peak,
+                             frac_tensor_sustained=tops / (2.0 * peaks["bf16_tflops_sustained"]),
+                             frac_nominal_4500=tops / 4500,
+                             channel_mm_u8_ms=ms_u8, channel_mm_u8_tops=2.0 * m * n * k / ms_u8 / 1e9,
+                             channel_mm_u8_vs_fused=ms_u8 / ms,
+                             cutlass_channel_mm_ms=ms_ws, cutlass_channel_mm_tops=2.0 * m * n * k / ms_ws / 1e9,
+                             quantize_us=ms_q * 1e3, quantize_us_min_max=_spread_us(ms_q),
+                             quantize_gbs=(3 * m * k + 4 * m) / ms_q / 1e6,
+                             quantize_frac_hbm=(3 * m * k + 4 * m) / ms_q / 1e6 / hbm)
         del wd, x, xs, out, codes
     # the SwiGLU + quantizer between the two prefill GEMMs: [4096, 2*17408] BF16 -> INT8 [4096, 17408]
     m, k = 4096, 17408
@@ -478,8 +593,11 @@ def other_configs(ops, workloads, device, peaks):
     ms_q = _time_graph(lambda i: ops.quantize_grouped4096(xs[i % 2], codes, scales), 20)
     ms = _time_graph(lambda i: ops.grouped_channel_mm(codes, wd, scales, sw, out), 10)
     tops = 2.0 * m * n * groups * 4096 / ms / 1e9
-    results["grouped"] = dict(gemm_ms=ms, tops=tops, frac_tensor=tops / tensor_peak, frac_nominal_4500=tops / 4500,
-                              quantize_us=ms_q * 1e3, quantize_gbs=(3 * m * groups * 4096 + 4 * m * groups) / ms_q / 1e6)
+    results["grouped"] = dict(gemm_ms=ms, gemm_ms_min_max=[ms.lo, ms.hi], tops=tops, frac_tensor=tops / tensor_peak,
+                              frac_tensor_sustained=tops / (2.0 * peaks["bf16_tflops_sustained"]), frac_nominal_4500=tops / 4500,
+                              quantize_us=ms_q * 1e3, quantize_us_min_max=_spread_us(ms_q),
+                              quantize_gbs=(3 * m * groups * 4096 + 4 * m * groups) / ms_q / 1e6,
+                              quantize_frac_hbm=(3 * m * groups * 4096 + 4 * m * groups) / ms_q / 1e6 / hbm)
     del xs, wd, codes, out
     # block-32 (Q8_0) W8A8 through the C ABI, at the shapes of the reference's benchmark
     # (benchmarks/benchmark_q8_block_int8.py:44: n=1024, k=4096); quantizer + product per call
@@ -559,8 +677,9 @@ def main():
     parser.add_argument("--profile-only", action="store_true",
                         help="run --steps launches of the workload's kernels with no timing (for ncu captures)")
     parser.add_argument("--schedule", type=int, default=0)
-    parser.add_argument("--gather", choices=["fused", "nccl"], default="fused",
-                        help="N>1: peer stores from the GEMM epilogue, or a separate NCCL all-gather")
+    parser.add_argument("--gather", choices=["fused", "fused_nccl_barrier", "nccl"], default="fused",
+                        help="N>1: peer stores from the GEMM epilogue (closed inside the kernel, or by an NCCL "
+                             "barrier), or a separate NCCL all-gather")
     parser.add_argument("--chunks", type=int, default=4,
                         help="--gather nccl: row chunks whose gather overlaps the next GEMM")
     parser.add_argument("--no-extra", action="store_true", help="skip the other benchmark configs")

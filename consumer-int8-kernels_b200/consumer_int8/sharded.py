@@ -5,18 +5,27 @@ parallel and gathers the result (benchmarks/microbench.py:187 "column parallel +
 Here rank r owns ``w[r*N/G:(r+1)*N/G]`` and its channel scales, the activations are replicated,
 every rank quantizes them itself (cheap next to the GEMM) and computes a BF16 ``[M, N/G]`` column
 block; only that BF16 block crosses NVLink, and afterwards the whole output is on every rank.
-Two ways to move it:
+Ways to move it (``mode``):
 
-* ``mode="fused"`` (default on CUDA): the gathered buffers live in symmetric memory, every rank
-  maps its peers' buffers, and the GEMM's epilogue stores each finished tile into block ``rank`` of
-  every rank's buffer (``ops.fused_channel_mm_gather``), so the transfers overlap the main loop and
-  no communication kernel competes with the persistent GEMM for SMs. A barrier ends the call.
-* ``mode="nccl"``: the GEMM writes its block locally and one NCCL all-gather moves it.
+* ``"fused"`` (the default on more than one GPU): the gathered buffers live in symmetric memory,
+  every rank maps its peers' buffers, and the GEMM's epilogue stores each finished tile into block
+  ``rank`` of every rank's buffer (``ops.fused_channel_mm_gather_sync``), so the transfers overlap the
+  main loop and no communication kernel competes with the persistent GEMM for SMs. The kernel ends
+  with a rendezvous over arrival counters in symmetric memory: when it returns on a rank, that rank's
+  buffer is complete, and no collective follows. The layer owns TWO sets of buffers and alternates
+  between them, so a rank that is already in its next call never writes into a result that a peer
+  is still reading: the tensor ``forward`` returns stays valid until the second-next ``forward``.
+* ``"fused_nccl_barrier"``: the same stores, closed by a small stream-ordered NCCL all-reduce instead
+  of the in-kernel rendezvous (the first form of this path; kept for comparison).
+* ``"nccl"``: the GEMM writes its block locally and one NCCL all-gather moves it.
+* ``"none"``: no gather at all: the result stays column-sharded, ``[M, N/G]`` per rank in block ``rank``
+  of the returned buffer. A row-parallel layer that follows (the down projection after a column-
+  parallel gate/up) consumes exactly that, and nothing crosses NVLink.
 
 Layout of the gathered output: ``[chunks, G, M/chunks, N/G]``. Column blocks of a row-major
 ``[M, N]`` matrix are not contiguous, so each rank's block is kept contiguous instead and the
-gather is done in place (a rank writes its block straight into its slot). ``chunks > 1`` splits
-the rows so that the gather of a finished row chunk overlaps the GEMM of the next one on a
+gather is done in place (a rank writes its block straight into its slot). ``chunks > 1`` (NCCL mode)
+splits the rows so that the gather of a finished row chunk overlaps the GEMM of the next one on a
 second stream. ``ShardPlan.row_major`` gives the ``[M, N]`` view as a copy when a caller needs it.
 
 The bookkeeping (``ShardPlan``) is plain Python and is tested with CPU ranks over gloo; the
@@ -84,15 +93,19 @@ class ShardPlan:
         return gathered.permute(0, 2, 1, 3).reshape(self.m, self.n)
 
 
+MODES = ("fused", "fused_nccl_barrier", "nccl", "none")
+
+
 class ColumnShardedLinear:
     """quantize_rows -> fused_channel_mm on this rank's channels -> all-gather of the BF16 block.
 
-    All buffers are allocated once here; ``forward`` allocates nothing.
+    All buffers are allocated once here; ``forward`` allocates nothing. ``mode=None`` picks
+    ``"fused"`` for CUDA weights on more than one rank and ``"nccl"`` otherwise.
     """
 
     def __init__(self, plan: ShardPlan, w_shard: torch.Tensor, w_scale_shard: torch.Tensor,
                  group: dist.ProcessGroup | None = None, schedule: int = 0, operators=None,
-                 mode: str = "nccl"):
+                 mode: str | None = None):
         if operators is None:
             from . import ops as operators  # the compiled operators; there is no fallback
 
@@ -107,26 +120,41 @@ class ColumnShardedLinear:
         device = w_shard.device
         self.codes = torch.empty(plan.m, plan.k, dtype=torch.int8, device=device)
         self.scales = torch.empty(plan.m, dtype=torch.float32, device=device)
-        if mode not in ("nccl", "fused"):
-            raise ValueError("mode must be 'nccl' or 'fused'")
+        if mode is None:
+            mode = "fused" if plan.world > 1 and device.type == "cuda" else "nccl"
+        if mode not in MODES:
+            raise ValueError(f"mode must be one of {MODES}")
         self.mode = mode if plan.world > 1 else "nccl"
-        self.peer_ptrs = None
-        if self.mode == "fused":
+        self.calls = 0
+        self._sets = []            # fused modes: two sets of (gathered, peer_ptrs, signal_ptrs, state, handles)
+        if self.mode in ("fused", "fused_nccl_barrier"):
             if plan.chunks != 1:
                 raise ValueError("the fused gather overlaps tile by tile; use chunks=1")
             if plan.shard_n % 8:
                 raise ValueError("the fused gather needs N/G % 8 == 0")
             import torch.distributed._symmetric_memory as symm_mem
 
-            flat = symm_mem.empty(plan.world * plan.m * plan.shard_n, dtype=torch.bfloat16, device=device)
-            handle = symm_mem.rendezvous(flat, group=group if group is not None else dist.group.WORLD)
-            self._symm_handle = handle          # keeps the peer mappings alive
-            self.peer_ptrs = torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64)
-            self.gathered = flat.view(plan.gathered_shape)
+            where = group if group is not None else dist.group.WORLD
+            for _ in range(2):
+                flat = symm_mem.empty(plan.world * plan.m * plan.shard_n, dtype=torch.bfloat16, device=device)
+                handle = symm_mem.rendezvous(flat, group=where)
+                counters = symm_mem.empty(8, dtype=torch.int64, device=device)   # one arrival counter per source rank
+                counters.zero_()
+                counter_handle = symm_mem.rendezvous(counters, group=where)
+                self._sets.append(dict(
+                    gathered=flat.view(plan.gathered_shape),
+                    peer_ptrs=torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64),
+                    signal_ptrs=torch.tensor([int(p) for p in counter_handle.buffer_ptrs], dtype=torch.int64),
+                    state=torch.zeros(2, dtype=torch.int64, device=device),
+                    keep=(handle, counter_handle, counters),     # keeps the peer mappings alive
+                ))
+            torch.cuda.synchronize(device)
+            dist.barrier(group=group)       # every rank's counters are zero before anybody signals
+            self.gathered = self._sets[0]["gathered"]
             self._barrier_word = torch.zeros(1, dtype=torch.float32, device=device)
         else:
             self.gathered = torch.empty(plan.gathered_shape, dtype=torch.bfloat16, device=device)
-        overlap = plan.chunks > 1 and plan.world > 1 and device.type == "cuda"
+        overlap = self.mode == "nccl" and plan.chunks > 1 and plan.world > 1 and device.type == "cuda"
         self.comm_stream = torch.cuda.Stream(device=device) if overlap else None
         self._chunk_done = [torch.cuda.Event() for _ in range(plan.chunks)] if self.comm_stream else []
 
@@ -144,17 +172,24 @@ class ColumnShardedLinear:
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         plan = self.plan
-        if plan.world == 1:
+        if plan.world == 1 or self.mode == "none":
             self.compute(x)
             return self.gathered
         self.ops.quantize_rows(x, self.codes, self.scales)
-        if self.mode == "fused":
-            # every rank writes its block into every rank's buffer; the barrier orders those peer
-            # writes before any rank reads. A rank must not start its next forward while a peer is
-            # still reading the previous result (alternate two layers, or barrier before the call).
-            self.ops.fused_channel_mm_gather(self.codes, self.w, self.scales, self.w_scale,
-                                             self.gathered[0], self.peer_ptrs, plan.rank, self.schedule)
-            dist.all_reduce(self._barrier_word, group=self.group)   # stream-ordered, no host sync
+        if self.mode in ("fused", "fused_nccl_barrier"):
+            # every rank writes its block into every rank's buffer; the two sets alternate so that a
+            # rank already in its next call cannot overwrite a result a peer still reads
+            current = self._sets[self.calls % 2]
+            self.calls += 1
+            self.gathered = current["gathered"]
+            if self.mode == "fused":
+                self.ops.fused_channel_mm_gather_sync(self.codes, self.w, self.scales, self.w_scale, self.gathered[0],
+                                                      current["peer_ptrs"], current["signal_ptrs"], current["state"],
+                                                      plan.rank, self.schedule)
+            else:
+                self.ops.fused_channel_mm_gather(self.codes, self.w, self.scales, self.w_scale, self.gathered[0],
+                                                 current["peer_ptrs"], plan.rank, self.schedule)
+                dist.all_reduce(self._barrier_word, group=self.group)   # stream-ordered, no host sync
             return self.gathered
         main = torch.cuda.current_stream() if self.comm_stream is not None else None
         for c in range(plan.chunks):

@@ -126,7 +126,9 @@ void boxed_mm(StableIValue* stack, uint64_t, uint64_t) {
                       out.size(0) == m && out.size(1) == n,
                   "Wrong scale or output shapes");
   STD_TORCH_CHECK(a.numel() <= kIntMax && w.numel() <= kIntMax, "Matrix too large");
-  STD_TORCH_CHECK(address(a) % 16 == 0 && address(w) % 16 == 0, "Matrix operands must be 16-byte aligned");
+  // the reference reads both operands as 32-bit words and asks for nothing more; operands that are
+  // not 16-byte aligned take the library's plain word-wise kernel instead of the TMA paths
+  STD_TORCH_CHECK(address(a) % 4 == 0 && address(w) % 4 == 0, "Matrix operands must be 4-byte aligned");
   torch::stable::accelerator::DeviceGuard guard(device);
   launched(ci8_channel_mm(static_cast<int8_t*>(a.data_ptr()), static_cast<uint8_t*>(w.data_ptr()),
                           static_cast<float*>(sa.data_ptr()), sw.data_ptr(), out.data_ptr(), m, n, k,
@@ -298,14 +300,17 @@ void boxed_gate_up_silu_mm(StableIValue* stack, uint64_t, uint64_t) {
                                stream_for(device)));
 }
 
-// Additive operator: this rank's output-channel shard of fused_channel_mm, written straight into
+// Additive operators: this rank's output-channel shard of fused_channel_mm, written straight into
 // block `rank` of every rank's gathered buffer [world, M, N/world] (peer-mapped symmetric memory).
-// peer_ptrs is a CPU INT64 tensor holding the device address of every rank's buffer.
-void boxed_fused_mm_gather(StableIValue* stack, uint64_t, uint64_t) {
+// peer_ptrs is a CPU INT64 tensor holding the device address of every rank's buffer. The _sync form
+// also takes signal_ptrs (CPU INT64, the address of every rank's arrival counters) and state (INT64
+// [2] on this device) and ends with the in-kernel cross-GPU rendezvous.
+void gather_common(StableIValue* stack, bool sync) {
   auto a = to<Tensor>(stack[0]), w = to<Tensor>(stack[1]);
   auto sa = to<Tensor>(stack[2]), sw = to<Tensor>(stack[3]);
   auto gathered = to<Tensor>(stack[4]), peer_ptrs = to<Tensor>(stack[5]);
-  const int64_t rank = to<int64_t>(stack[6]), schedule = to<int64_t>(stack[7]);
+  const int base = sync ? 8 : 6;
+  const int64_t rank = to<int64_t>(stack[base]), schedule = to<int64_t>(stack[base + 1]);
   const int device = a.get_device_index();
   check(a, ScalarType::Char, device);
   check(w, ScalarType::Char, device);
@@ -330,12 +335,31 @@ void boxed_fused_mm_gather(StableIValue* stack, uint64_t, uint64_t) {
   void* buffers[8];
   for (int64_t r = 0; r < world; ++r) buffers[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(addresses[r]));
   STD_TORCH_CHECK(address(a) % 16 == 0 && address(w) % 16 == 0, "Matrix operands must be 16-byte aligned");
+  if (!sync) {
+    torch::stable::accelerator::DeviceGuard guard(device);
+    launched(ci8_fused_channel_mm_gather(static_cast<int8_t*>(a.data_ptr()), static_cast<int8_t*>(w.data_ptr()),
+                                         static_cast<float*>(sa.data_ptr()), sw.data_ptr(), buffers,
+                                         static_cast<int>(world), static_cast<int>(rank), m, n, k,
+                                         static_cast<int>(schedule), stream_for(device)));
+    return;
+  }
+  auto signal_ptrs = to<Tensor>(stack[6]), state = to<Tensor>(stack[7]);
+  check(state, ScalarType::Long, device);
+  STD_TORCH_CHECK(state.numel() == 2, "state must hold two INT64 words");
+  STD_TORCH_CHECK(!signal_ptrs.is_cuda() && signal_ptrs.is_contiguous() && signal_ptrs.scalar_type() == ScalarType::Long &&
+                      signal_ptrs.dim() == 1 && signal_ptrs.size(0) == world,
+                  "signal_ptrs must be a contiguous CPU INT64 vector with one entry per rank");
+  const int64_t* signal_addresses = static_cast<const int64_t*>(signal_ptrs.data_ptr());
+  void* signals[8];
+  for (int64_t r = 0; r < world; ++r) signals[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(signal_addresses[r]));
   torch::stable::accelerator::DeviceGuard guard(device);
-  launched(ci8_fused_channel_mm_gather(static_cast<int8_t*>(a.data_ptr()), static_cast<int8_t*>(w.data_ptr()),
-                                       static_cast<float*>(sa.data_ptr()), sw.data_ptr(), buffers,
-                                       static_cast<int>(world), static_cast<int>(rank), m, n, k,
-                                       static_cast<int>(schedule), stream_for(device)));
+  launched(ci8_fused_channel_mm_gather_sync(static_cast<int8_t*>(a.data_ptr()), static_cast<int8_t*>(w.data_ptr()),
+                                            static_cast<float*>(sa.data_ptr()), sw.data_ptr(), buffers, signals,
+                                            state.data_ptr(), static_cast<int>(world), static_cast<int>(rank), m, n, k,
+                                            static_cast<int>(schedule), stream_for(device)));
 }
+void boxed_fused_mm_gather(StableIValue* stack, uint64_t, uint64_t) { gather_common(stack, false); }
+void boxed_fused_mm_gather_sync(StableIValue* stack, uint64_t, uint64_t) { gather_common(stack, true); }
 }  // namespace
 
 STABLE_TORCH_LIBRARY(consumer_int8, m) {
@@ -352,6 +376,7 @@ STABLE_TORCH_LIBRARY(consumer_int8, m) {
   m.def("dynamic_channel_mm(Tensor x, Tensor w, Tensor w_scale, Tensor(a!) codes, Tensor(b!) scales, Tensor(c!) out) -> ()");
   m.def("gate_up_silu_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) out) -> ()");
   m.def("fused_channel_mm_gather(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) gathered, Tensor peer_ptrs, int rank, int schedule=0) -> ()");
+  m.def("fused_channel_mm_gather_sync(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) gathered, Tensor peer_ptrs, Tensor signal_ptrs, Tensor(b!) state, int rank, int schedule=0) -> ()");
 }
 STABLE_TORCH_LIBRARY_IMPL(consumer_int8, CUDA, m) {
   m.impl("silu_mul", &boxed_silu_mul);
@@ -367,6 +392,7 @@ STABLE_TORCH_LIBRARY_IMPL(consumer_int8, CUDA, m) {
   m.impl("gate_up_silu_mm", &boxed_gate_up_silu_mm);
   m.impl("dynamic_channel_mm", &boxed_dynamic_mm);
   m.impl("fused_channel_mm_gather", &boxed_fused_mm_gather);
+  m.impl("fused_channel_mm_gather_sync", &boxed_fused_mm_gather_sync);
 }
 extern "C" PyObject* PyInit__C() {
   static PyModuleDef module = {PyModuleDef_HEAD_INIT, "_C", nullptr, -1, nullptr};

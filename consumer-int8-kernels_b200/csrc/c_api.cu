@@ -112,21 +112,12 @@ cudaError_t make_bf16_map(CUtensorMap* map, const void* base, uint64_t rows, uin
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-// `outputs` lists every destination of the BF16 result (this GPU's buffer and, for the gathering
-// form, the matching block in each peer's buffer). When the row pitch allows it they are written
-// with TMA tile stores; otherwise the single local output takes the direct-store path.
+// Fills the tiling of a launch into p (tiles_m, group_m, tile_n, tiles_n, wide_tiles, split, full_tiles,
+// total_items, out_n) for `workers` persistent CTAs (CTA pairs for kCtas == 2). p.tile_n > 0 on entry
+// forces that width (a schedule); num_outputs > 1 is the gathering form.
 template <int kCtas, int kMode>
-cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cudaStream_t stream,
-                        void* const* outputs = nullptr, int num_outputs = 0) {
+void plan_tiles(GemmParams& p, int num_outputs, long long workers) {
   using Cfg = GemmConfig<kCtas, kMode>;
-  static std::atomic<uint64_t> smem_done{0};
-  auto kernel = gemm_i8_kernel<kCtas, kMode>;
-  cudaError_t err = ensure_smem(kernel, Cfg::kSmemBytes, smem_done);
-  if (err != cudaSuccess) return err;
-
-  GemmParams p = base;
-  const int sms = sm_count();
-  const long long workers = kCtas == 2 ? sms / 2 : sms;
   p.tiles_m = (p.m + Cfg::kBlockM * kCtas - 1) / (Cfg::kBlockM * kCtas);
   // Tile width and last-wave slicing. The persistent grid works through the tiles in waves of `workers`
   // equally long tiles, so the time is about waves x (tile width + a per-tile overhead worth ~9 columns).
@@ -137,17 +128,17 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
   // but the slice still streams all of A through a ring sized for whole tiles).
   // The 224-wide tile runs ~3 % below the line (its last 64-column box straddles the tile edge and
   // leaves through direct stores) and cannot be sliced (112 is not a multiple of 32). Ties go to the
-  // wider tile. A schedule can force the width; the biased form keeps 240 channels + 16 ones rows,
+  // wider tile. A schedule can force the width; the biased form keeps 248 channels + 8 ones rows,
   // unsliced; the gathering form needs whole 64-column boxes (256 or 192 wide, slices of 128 or 64).
   int tile_n = 256, split = 1;
+  double best = 1e300;
+  const bool forced = p.tile_n > 0 && num_outputs <= 1;
   p.out_n = kMode == kModeSwiGLU ? p.n / 2 : p.n;
   if (kMode == kModeBiased) {
     tile_n = Cfg::kChannelsPerTile;
   } else if (kMode == kModeSwiGLU) {
     tile_n = 256;   // a tile is 128 gate channels and their 128 up channels: whole, unsliced tiles only
   } else {
-    const bool forced = p.tile_n > 0 && num_outputs <= 1;
-    double best = 1e300;
     for (int cand = 256; cand >= 192; cand -= 32) {
       if (forced && cand != p.tile_n) continue;
       if (cand % 64 != 0 && num_outputs > 1) continue;
@@ -162,27 +153,99 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
       }
     }
   }
+  // Third remedy, mixed widths: cut every row stripe's channels (in units of 32) into `count` tiles whose
+  // widths differ by at most one unit (192 / 224 / 256 columns), with `count` such that the tiles fill
+  // whole waves. The load of the busiest worker is found by walking the kernel's own item order. Taken
+  // only when it beats the uniform choices by 3 % in the model; one local destination only (a 64-column
+  // store box must not straddle tiles of the gathering form), no forced schedule, and only for
+  // problems of a few waves (beyond that a partial last wave is noise, and the walk would cost time).
+  int mixed_count = 0, mixed_base = 0, mixed_wide = 0;
+  // rows of A per raster group: about 32 MiB of activations, so they stay in L2
+  const long long group_rows = (32ll << 20) / (static_cast<long long>(p.k) * p.groups);
+  p.group_m = static_cast<int>(group_rows / (Cfg::kBlockM * kCtas));
+  if (p.group_m < 1) p.group_m = 1;
+  if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
+  if ((kMode == kModeFused || kMode == kModeWorkspace || kMode == kModeGrouped) && num_outputs <= 1 && !forced &&
+      workers <= 256) {
+    // the decision depends on the shape only: remember the last one per thread
+    struct Memo { int m, n, group_m, workers, count, base, wide; };
+    thread_local Memo memo = {0, 0, 0, 0, 0, 0, 0};
+    if (memo.m == p.m && memo.n == p.n && memo.group_m == p.group_m && memo.workers == workers) {
+      mixed_count = memo.count; mixed_base = memo.base; mixed_wide = memo.wide;
+    } else {
+      const int units = (p.n + 31) / 32;
+      double best_mixed = 1e300;
+      for (int count = (units + 7) / 8; count <= units / 6; ++count) {
+        const int base = units / count, wide = units % count;
+        const long long tiles = static_cast<long long>(p.tiles_m) * count;
+        if (wide == 0 || base + 1 > 8 || tiles > 12 * workers) continue;   // uniform widths are covered above
+        GemmParams trial = p;
+        trial.tile_n = base * 32; trial.tiles_n = count; trial.wide_tiles = wide;
+        trial.split = 1; trial.full_tiles = trial.total_items = static_cast<int>(tiles);
+        double load[256] = {};
+        double busiest = 0.0;
+        for (int item = 0; item < trial.total_items; ++item) {
+          int mt, nt, n_start, n_width;
+          bool alt;
+          tile_coords(trial, item, mt, nt, n_start, n_width, alt);
+          // a tile that is not a whole number of 64-column boxes pays the 224-wide tile's 3 %
+          double& mine = load[item % workers];
+          mine += (n_width + 9) * (n_width % 64 ? 1.03 : 1.0);
+          if (mine > busiest) busiest = mine;
+        }
+        if (busiest < best_mixed * 0.999) { best_mixed = busiest; mixed_count = count; mixed_base = base * 32; mixed_wide = wide; }
+      }
+      if (best_mixed >= best * 0.97) mixed_count = 0;
+      memo = Memo{p.m, p.n, p.group_m, static_cast<int>(workers), mixed_count, mixed_base, mixed_wide};
+    }
+  }
+  p.wide_tiles = 0;
+  if (mixed_count > 0) {
+    tile_n = mixed_base;
+    split = 1;
+    p.wide_tiles = mixed_wide;
+  }
   p.tile_n = tile_n;
-  p.tiles_n = (p.n + tile_n - 1) / tile_n;
+  p.tiles_n = mixed_count > 0 ? mixed_count : (p.n + tile_n - 1) / tile_n;
   {
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     p.split = split;
     p.full_tiles = split > 1 ? static_cast<int>(tiles - tiles % workers) : static_cast<int>(tiles);
     p.total_items = p.full_tiles + static_cast<int>(tiles - p.full_tiles) * split;
   }
-  const int w_box_rows = kMode == kModeBiased ? Cfg::kBRowsLoad : tile_n / kCtas;
+}
+
+// `outputs` lists every destination of the BF16 result (this GPU's buffer and, for the gathering
+// form, the matching block in each peer's buffer). When the row pitch allows it they are written
+// with TMA tile stores; otherwise the single local output takes the direct-store path.
+template <int kCtas, int kMode>
+cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cudaStream_t stream,
+                        void* const* outputs = nullptr, int num_outputs = 0, void* const* signals = nullptr,
+                        void* state = nullptr, int source = 0) {
+  using Cfg = GemmConfig<kCtas, kMode>;
+  static std::atomic<uint64_t> smem_done{0};
+  auto kernel = gemm_i8_kernel<kCtas, kMode>;
+  cudaError_t err = ensure_smem(kernel, Cfg::kSmemBytes, smem_done);
+  if (err != cudaSuccess) return err;
+
+  GemmParams p = base;
+  const int sms = sm_count();
+  plan_tiles<kCtas, kMode>(p, num_outputs, kCtas == 2 ? sms / 2 : sms);
+  const int tile_n = p.tile_n;
+  // biased form: the CTA that holds the ones rows loads kBRowsLoad channels; in a pair the first CTA loads
+  // kBRowsSmem through map_w and the second kBRowsLoad through the second map
+  const int w_box_rows = kMode == kModeBiased ? (kCtas == 2 ? Cfg::kBRowsSmem : Cfg::kBRowsLoad) : tile_n / kCtas;
   p.stage_tx = Cfg::kABytes + w_box_rows * Cfg::kBlockK;
-  // rows of A per raster group: about 32 MiB of activations, so they stay in L2
-  const long long group_rows = (32ll << 20) / (static_cast<long long>(p.k) * p.groups);
-  p.group_m = static_cast<int>(group_rows / (Cfg::kBlockM * kCtas));
-  if (p.group_m < 1) p.group_m = 1;
-  if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
   CUtensorMap map_a, map_w, map_w_slice;
   err = make_map(&map_a, a, static_cast<uint64_t>(p.m) * p.groups, p.k, Cfg::kBlockM);
   if (err != cudaSuccess) return err;
   err = make_map(&map_w, w, p.n, static_cast<uint64_t>(p.k) * p.groups, w_box_rows);
   if (err != cudaSuccess) return err;
-  const int slice_box_rows = p.split > 1 ? tile_n / p.split / kCtas : w_box_rows;
+  // the second weight box: a column slice of the last wave's tiles, or the wider tiles of the mixed form
+  const int slice_box_rows = kMode == kModeBiased ? Cfg::kBRowsLoad
+                             : p.wide_tiles > 0   ? (tile_n + 32) / kCtas
+                             : p.split > 1        ? tile_n / p.split / kCtas
+                                                  : w_box_rows;
   p.stage_tx_slice = Cfg::kABytes + slice_box_rows * Cfg::kBlockK;
   err = make_map(&map_w_slice, w, p.n, static_cast<uint64_t>(p.k) * p.groups, slice_box_rows);
   if (err != cudaSuccess) return err;
@@ -192,7 +255,7 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
     outputs = local_only;
     num_outputs = 1;
   }
-  bool tile_stores = kMode != kModeBiased && p.out_n % 8 == 0 && num_outputs <= kMaxOutputs;
+  bool tile_stores = p.out_n % 8 == 0 && num_outputs <= kMaxOutputs;
   for (int d = 0; d < num_outputs; ++d) tile_stores = tile_stores && aligned(outputs[d], 16);
   p.num_outputs = 0;
   if (tile_stores) {
@@ -201,6 +264,12 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
       if (err != cudaSuccess) return err;
     }
     p.num_outputs = num_outputs;
+    if (signals && state) {
+      // the gathering form closes with the in-kernel rendezvous over these counters
+      for (int d = 0; d < num_outputs; ++d) out_maps.signal[d] = static_cast<unsigned long long*>(signals[d]);
+      out_maps.state = static_cast<unsigned long long*>(state);
+      out_maps.source = source;
+    }
   } else if (num_outputs != 1 || kMode == kModeSwiGLU) {
     return cudaErrorInvalidValue;   // several destinations, and the SwiGLU form, need the tile-store path
   }
@@ -468,6 +537,47 @@ cudaError_t launch_gemv(const void* x, const int8_t* w, const void* sw, void* ou
   return cudaGetLastError();
 }
 
+// channel_mm for operands that are only 4-byte aligned (a view at an odd offset into a larger
+// buffer): TMA needs 16-byte aligned bases, the reference's kernel reads 32-bit words and accepts
+// such operands, so this plain kernel does too. One warp per (row, eight channels): the lanes walk K
+// in 32-bit words, dp4a on the activation word and the eight weight words (code+128 turned into the
+// signed code by flipping the top bit of every byte), a shuffle tree, the usual epilogue. Integer
+// sums are exact, so the result has the same bits as the tensor-core path. Slow, and only chosen
+// when the fast path cannot take the pointers.
+__global__ void __launch_bounds__(256)
+channel_mm_words_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict__ w, const float* __restrict__ sa,
+                        const __nv_bfloat16* __restrict__ sw, __nv_bfloat16* __restrict__ out, int m, int n, int k) {
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int groups = (n + 7) / 8;
+  const int row = static_cast<int>(warp / groups);
+  const int c0 = static_cast<int>(warp % groups) * 8;
+  if (row >= m) return;
+  const int* a_words = reinterpret_cast<const int*>(a + static_cast<size_t>(row) * k);
+  int acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int word = lane; word < k / 4; word += 32) {
+    const int av = __ldg(a_words + word);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (c0 + j < n) {
+        const unsigned wv = __ldg(reinterpret_cast<const unsigned*>(w + static_cast<size_t>(c0 + j) * k) + word);
+        acc[j] = __dp4a(av, static_cast<int>(wv ^ 0x80808080u), acc[j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], offset);
+  if (lane < 8 && c0 + lane < n) {
+    int mine = acc[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) mine = lane == j ? acc[j] : mine;
+    const float scaled = __fmul_rn(__fmul_rn(__int2float_rn(mine), sa[row]), __bfloat162float(sw[c0 + lane]));
+    out[static_cast<size_t>(row) * n + c0 + lane] = __float2bfloat16_rn(scaled);
+  }
+}
+
 // Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever arrives on. The
 // wait gives up after `deadline_ns`, raises the status bit and the kernel returns normally.
 __global__ void wait_timeout_selftest_kernel(unsigned long long deadline_ns, int* gave_up) {
@@ -480,6 +590,29 @@ __global__ void wait_timeout_selftest_kernel(unsigned long long deadline_ns, int
     const bool completed = mbar_wait(smem_u32(&barrier), 0u, &abort_flag, deadline_ns);
     *gave_up = completed ? 0 : 1;
   }
+}
+
+// The same for a rendezvous between the CTAs of a cluster: CTA 0 of a pair waits on a barrier that CTA 1
+// is supposed to arrive on remotely and, in this self-test, never does. The wait gives up after
+// `deadline_ns` and raises the cluster status bit; the closing cluster barrier keeps CTA 1 around
+// until then, as the split-K kernel's teardown does.
+__global__ void __cluster_dims__(2, 1, 1) cluster_timeout_selftest_kernel(unsigned long long deadline_ns, int* gave_up) {
+  __shared__ alignas(8) unsigned long long barrier;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&barrier), 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (cluster_ctarank() == 0 && threadIdx.x == 0) {
+    const bool completed = mbar_wait<true, kStatusClusterTimeout>(smem_u32(&barrier), 0u, &abort_flag, deadline_ns);
+    *gave_up = completed ? 0 : 1;
+  }
+  cluster_arrive();
+  cluster_wait();
 }
 
 }  // namespace
@@ -543,7 +676,7 @@ cudaError_t q8_static_scratch(unsigned char** out) {
 // ====================================================================== C ABI
 extern "C" {
 
-int ci8_abi_version(void) { return 1; }
+int ci8_abi_version(void) { return 2; }
 
 const char* ci8_error_string(int code) {
   return code == 0 ? "success" : cudaGetErrorString(static_cast<cudaError_t>(code));
@@ -640,9 +773,17 @@ int ci8_cutlass_channel_mm(const int8_t* a, const int8_t* w, const float* a_scal
 
 int ci8_channel_mm(const int8_t* a, const uint8_t* w, const float* a_scale, const void* w_scale, void* out,
                    int m, int n, int k, ci8_stream_t stream) {
-  if (!a || !w || !a_scale || !w_scale || !out || !gemm_geometry_ok(m, n, k) || !aligned(a, 16) || !aligned(w, 16))
+  if (!a || !w || !a_scale || !w_scale || !out || !gemm_geometry_ok(m, n, k) || !aligned(a, 4) || !aligned(w, 4) ||
+      static_cast<long long>(m) * n > INT32_MAX)
     return kInvalid;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (!aligned(a, 16) || !aligned(w, 16)) {
+    // operands the TMA paths cannot take (the reference accepts any 4-byte aligned pointer)
+    const long long warps = static_cast<long long>(m) * ((n + 7) / 8);
+    channel_mm_words_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, s>>>(
+        a, w, a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), m, n, k);
+    return cudaGetLastError();
+  }
   if (m <= kDecodeMaxRows) {
     DecodeParams p{a, a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out),
                    nullptr, m, n, k, 0};
@@ -650,7 +791,7 @@ int ci8_channel_mm(const int8_t* a, const uint8_t* w, const float* a_scale, cons
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
                m, n, k, 1, 0, 0, 0, 0, 0, 0};
-  return launch_gemm<1, kModeBiased>(a, w, p, s);
+  return m > 128 ? launch_gemm<2, kModeBiased>(a, w, p, s) : launch_gemm<1, kModeBiased>(a, w, p, s);
 }
 
 int ci8_channel_gemv(const void* x, const int8_t* w, const void* w_scale, void* out, int m, int n, int k,
@@ -714,33 +855,60 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
   return m > 128 ? launch_gemm<2, kModeGrouped>(codes, w, p, s) : launch_gemm<1, kModeGrouped>(codes, w, p, s);
 }
 
-int ci8_fused_channel_mm_gather(const int8_t* a, const int8_t* w, const float* a_scale, const void* w_scale,
-                                void* const* gathered, int world, int rank, int m, int n_shard, int k,
-                                int schedule, ci8_stream_t stream) {
+namespace {
+// Shared by the two gathering entry points. destination d = the [m, n_shard] block number `rank` of
+// peer (rank + d) % world: every rank starts with its own buffer and walks the peers in a different
+// order, which spreads the NVLink traffic.
+int gather_impl(const int8_t* a, const int8_t* w, const float* a_scale, const void* w_scale, void* const* gathered,
+                void* const* signals, void* state, int world, int rank, int m, int n_shard, int k, int schedule,
+                ci8_stream_t stream) {
   if (!a || !w || !a_scale || !w_scale || !gathered || world <= 0 || world > kMaxOutputs || rank < 0 ||
       rank >= world || !gemm_geometry_ok(m, n_shard, k) || n_shard % 8 != 0 || schedule < 0 || schedule > 6 ||
       !aligned(a, 16) || !aligned(w, 16) || static_cast<long long>(m) * n_shard * world > INT32_MAX)
     return kInvalid;
-  // destination d = the [m, n_shard] block number `rank` of peer (rank + d) % world: every rank starts
-  // with its own buffer and walks the peers in a different order, which spreads the NVLink traffic
   void* outputs[kMaxOutputs];
+  void* counters[kMaxOutputs];
   const size_t block_bytes = static_cast<size_t>(m) * n_shard * 2;
   for (int d = 0; d < world; ++d) {
     void* base = gathered[(rank + d) % world];
     if (!base || !aligned(base, 16)) return kInvalid;
     outputs[d] = static_cast<char*>(base) + block_bytes * rank;
+    counters[d] = signals ? signals[(rank + d) % world] : nullptr;
+    if (signals && (!counters[d] || !aligned(counters[d], 8))) return kInvalid;
   }
   GemmParams p{a_scale, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(outputs[0]), nullptr,
                m, n_shard, k, 1, 0, 0, 0, 0, 0, 0};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const bool pair = schedule == 0 ? m > 128 : (schedule % 2 == 0);
-  return pair ? launch_gemm<2, kModeFused>(a, w, p, s, outputs, world)
-              : launch_gemm<1, kModeFused>(a, w, p, s, outputs, world);
+  void* const* sig = signals ? counters : nullptr;
+  return pair ? launch_gemm<2, kModeFused>(a, w, p, s, outputs, world, sig, state, rank)
+              : launch_gemm<1, kModeFused>(a, w, p, s, outputs, world, sig, state, rank);
+}
+}  // namespace
+
+int ci8_fused_channel_mm_gather(const int8_t* a, const int8_t* w, const float* a_scale, const void* w_scale,
+                                void* const* gathered, int world, int rank, int m, int n_shard, int k,
+                                int schedule, ci8_stream_t stream) {
+  return gather_impl(a, w, a_scale, w_scale, gathered, nullptr, nullptr, world, rank, m, n_shard, k, schedule, stream);
+}
+
+int ci8_fused_channel_mm_gather_sync(const int8_t* a, const int8_t* w, const float* a_scale, const void* w_scale,
+                                     void* const* gathered, void* const* signals, void* state, int world, int rank,
+                                     int m, int n_shard, int k, int schedule, ci8_stream_t stream) {
+  if (!signals || !state || !aligned(state, 8)) return kInvalid;
+  return gather_impl(a, w, a_scale, w_scale, gathered, signals, state, world, rank, m, n_shard, k, schedule, stream);
 }
 
 int ci8_selftest_wait_timeout(unsigned deadline_us, int* gave_up, ci8_stream_t stream) {
   if (!gave_up || deadline_us == 0 || deadline_us > 1000000) return kInvalid;   // at most one second
   wait_timeout_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<unsigned long long>(deadline_us) * 1000ull, gave_up);
+  return cudaGetLastError();
+}
+
+int ci8_selftest_cluster_timeout(unsigned deadline_us, int* gave_up, ci8_stream_t stream) {
+  if (!gave_up || deadline_us == 0 || deadline_us > 1000000) return kInvalid;   // at most one second
+  cluster_timeout_selftest_kernel<<<2, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<unsigned long long>(deadline_us) * 1000ull, gave_up);
   return cudaGetLastError();
 }
@@ -805,6 +973,23 @@ int ci8_q8_block_mm_static(const void* x, const int8_t* w, const void* sw, void*
 }
 
 int ci8_q8_block_static_max_values(void) { return static_cast<int>(kQ8StaticMaxValues); }
+
+int ci8_gemm_tile_plan(int m, int n, int k, int groups, int* plan) {
+  if (!plan || m <= 0 || n <= 0 || k <= 0 || groups <= 0) return kInvalid;
+  GemmParams p{nullptr, nullptr, nullptr, nullptr, m, n, k, groups, 0, 0, 0, 0, 0, 0};
+  const int sms = sm_count();
+  const bool pair = m > 128;
+  if (groups > 1) {
+    if (pair) plan_tiles<2, kModeGrouped>(p, 1, sms / 2); else plan_tiles<1, kModeGrouped>(p, 1, sms);
+  } else {
+    if (pair) plan_tiles<2, kModeFused>(p, 1, sms / 2); else plan_tiles<1, kModeFused>(p, 1, sms);
+  }
+  plan[0] = p.tile_n;
+  plan[1] = p.tiles_n;
+  plan[2] = p.wide_tiles;
+  plan[3] = p.split;
+  return 0;
+}
 
 // Test hook: the streaming kernel with a forced split-K factor (1, 2 or 4; at most 2 above 16 rows);
 // weights_biased != 0 selects the UINT8 form. Same contract as ci8_fused_channel_mm / ci8_channel_mm.

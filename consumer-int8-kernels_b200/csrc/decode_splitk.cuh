@@ -116,7 +116,10 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
   auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kMaxStages + s); };
   const uint32_t done_bar = bar_base + 8u * (2 * Cfg::kMaxStages);
   auto ready_bar = [&](int s) { return bar_base + 8u * (2 * Cfg::kMaxStages + 1 + s); };   // dynamic form
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_region + 8 * (3 * Cfg::kMaxStages + 1));
+  // split-K: the other CTAs of the cluster arrive here (remotely) once their partial sums are in this
+  // CTA's reduce buffer; only the leader's copy is used
+  const uint32_t reduce_bar = bar_base + 8u * (3 * Cfg::kMaxStages + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_region + 8 * (3 * Cfg::kMaxStages + 2));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* scale_tab = reinterpret_cast<float*>(bar_region + Cfg::kBarrierBytes);          // [kMaxSlab]
   int32_t* row_sums = reinterpret_cast<int32_t*>(scale_tab + Cfg::kMaxSlab);             // [warp][16]
@@ -140,6 +143,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
       if constexpr (kDynamic) mbar_init(ready_bar(s), Cfg::kEpilogueWarps);
     }
     mbar_init(done_bar, 1);
+    if constexpr (kSplit > 1) mbar_init(reduce_bar, (kSplit - 1) * Cfg::kEpilogueWarps);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&map_w);
@@ -152,6 +156,10 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
+  // Split-K, first cluster phase: every thread announces that its CTA's barriers are initialised. The
+  // matching wait stands in front of the first access to another CTA's shared memory (the epilogue
+  // warps) or in the teardown (everybody else), so nobody blocks here.
+  if constexpr (kSplit > 1) cluster_arrive();
   const uint32_t tmem_base = *tmem_slot;
   // Everything above touched only shared memory, TMEM and kernel parameters; from here on global
   // memory is read and written, so the previous kernel in the stream must have finished.
@@ -382,7 +390,9 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
       }
     };
 
+    bool partials_in = true;
     if constexpr (kSplit > 1) {
+      cluster_wait();   // first phase: every CTA of the cluster has initialised its barriers
       if (rank != 0) {
         // push this CTA's partials into the leader's reduce buffer: [rank-1][channel][row]
         const uint32_t remote = map_to_cta(smem_u32(reduce_buf), 0);
@@ -395,11 +405,16 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
             }
           }
         });
+        // the stores above are released to the leader by this warp's arrival on its barrier
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(reduce_bar, 0);
+      } else {
+        // The leader waits for every epilogue warp of every other CTA, with a deadline like every other
+        // wait: a peer that never delivers raises the cluster status bit and this CTA writes nothing.
+        partials_in = __all_sync(0xffffffffu, mbar_wait<true, kStatusClusterTimeout>(reduce_bar, 0u, abort_flag));
       }
-      cluster_arrive();
-      cluster_wait();
     }
-    if (rank == 0) {
+    if (rank == 0 && partials_in) {
       for_each_chunk([&](int chunk, int32_t (&acc)[32]) {
         if constexpr (kSplit > 1) {
           if (real_row) {
@@ -455,10 +470,13 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
     }
   }
   if constexpr (kSplit > 1) {
-    if (!(kRows == 16 ? (warp == 0 || warp == 4) : warp < 8)) {   // the epilogue warps passed the cluster rendezvous above
-      cluster_arrive();
-      cluster_wait();
-    }
+    // the epilogue warps completed the first cluster phase above, everybody else does it here
+    if (!(kRows == 16 ? (warp == 0 || warp == 4) : warp < 8)) cluster_wait();
+    // Second phase: no CTA leaves while a peer may still write into its shared memory or arrive on its
+    // barrier. This hardware barrier has no deadline of its own; it is bounded because every wait on a
+    // peer's way here is.
+    cluster_arrive();
+    cluster_wait();
   }
   tcgen05_fence_before();
   __syncthreads();

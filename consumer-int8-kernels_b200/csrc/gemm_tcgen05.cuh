@@ -21,9 +21,11 @@
 //   kModeFused      signed INT8 weights, BF16 output only (fused_channel_mm)
 //   kModeWorkspace  as fused, and the INT32 accumulators are also written to a caller buffer
 //                   (cutlass_channel_mm)
-//   kModeBiased     UINT8 weights holding code+128 (channel_mm): the weight tile carries 240
-//                   channels plus 16 rows of ones, so accumulator column 240 is sum_k a[m,k]
-//                   and the signed product is acc - 128 * that sum, still exact INT32
+//   kModeBiased     UINT8 weights holding code+128 (channel_mm): the weight tile carries 248
+//                   channels plus 8 rows of ones (one swizzle atom), so accumulator column 248 is
+//                   sum_k a[m,k] and the signed product is acc - 128 * that sum, still exact
+//                   INT32. In a CTA pair the second CTA holds the ones rows behind its 120
+//                   channels; the first one loads 128 channels
 //   kModeGrouped    K is G groups of 4096 with one activation scale per (group,row): each
 //                   group's INT32 accumulator is converted, scaled and added in FP32 in
 //                   ascending group order (separate multiply and add), then the channel
@@ -58,18 +60,31 @@ struct GemmParams {
   int group_m;                // row tiles per raster group (L2 reuse of the A rows)
   int num_outputs;            // TMA-store destinations in OutputMaps; 0 selects direct stores
   int tile_n;                 // output channels per tile: 256, or narrower (a multiple of 32) when that
-                              // packs the tiles into fewer, fuller waves; 240 for the biased form
+                              // packs the tiles into fewer, fuller waves; 248 for the biased form
   int stage_tx;               // bytes one CTA's TMA loads deliver per stage (A box + W box)
   int stage_tx_slice;         // the same for a column slice (A box + the narrower W box)
   int full_tiles;             // work items [0, full_tiles) are whole tiles (the complete waves)
   int split;                  // each tile of the last, partial wave is cut into `split` column slices
   int total_items;            // full_tiles + (tiles - full_tiles) * split
   int out_n;                  // columns of the output matrix: n, or n / 2 for kModeSwiGLU
+  int wide_tiles;             // mixed widths: the first wide_tiles channel tiles of every row stripe are
+                              // tile_n + 32 columns wide, the others tile_n (0: all tiles are tile_n wide)
 };
 
 // Tensor maps of the output destinations: BF16 [M,N] matrices, boxes of 64 columns x 32 rows.
+// The gathering form can also close with a cross-GPU rendezvous inside the kernel. signal[d] points
+// to kMaxOutputs arrival counters (64-bit, zero at first, never reset) in the memory of destination
+// d's GPU, one per source rank; signal[0] is this GPU's own set. Every CTA of rank `source` adds one
+// to counter `source` of every destination after its tile stores have completed, then waits until
+// each of its own GPU's counters shows that all CTAs of that rank have arrived for this call: when the
+// kernel ends, the whole gathered result is in this GPU's memory. state (two 64-bit words in this
+// GPU's memory, zero at first) counts the calls, so that a call can be replayed from a CUDA graph:
+// state[0] = completed calls, state[1] = CTAs of the running call that have left.
 struct OutputMaps {
   CUtensorMap map[kMaxOutputs];
+  unsigned long long* signal[kMaxOutputs];
+  unsigned long long* state;      // nullptr: no rendezvous, the caller orders a barrier after the call
+  int source;                     // this rank
 };
 
 template <int kCtas, int kMode>
@@ -77,10 +92,11 @@ struct GemmConfig {
   static constexpr int kBlockM = 128;                 // rows of A per CTA
   static constexpr int kTileN = 256;                  // accumulator columns per tile
   static constexpr int kBlockK = 128;                 // bytes of K per stage
-  static constexpr int kOnesRows = kMode == kModeBiased ? 16 : 0;
+  static constexpr int kOnesRows = kMode == kModeBiased ? 8 : 0;
   static constexpr int kChannelsPerTile = kTileN - kOnesRows;   // output channels per tile
   static constexpr int kBRowsSmem = kTileN / kCtas;   // weight rows held by one CTA
-  static constexpr int kBRowsLoad = kBRowsSmem - (kCtas == 1 ? kOnesRows : 0);
+  // weight rows loaded by the CTA that also holds the ones rows (the only CTA, or the second of a pair)
+  static constexpr int kBRowsLoad = kBRowsSmem - kOnesRows;
   static constexpr int kABytes = kBlockM * kBlockK;
   static constexpr int kBBytes = kBRowsSmem * kBlockK;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -93,7 +109,6 @@ struct GemmConfig {
   static constexpr int kStagingBytes = kEpiWarps * kStoreBufs * kStoreBoxBytes;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
-  static_assert(kMode != kModeBiased || kCtas == 1, "biased weights use the single-CTA tile");
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
@@ -105,25 +120,45 @@ struct GemmConfig {
 // into `split` column slices of tile_n/split accumulator columns that spread over the CTAs the wave
 // would leave idle. A slice still streams the full K extent of A, but its MMAs are narrower and take
 // about N/2 cycles each, so a half slice lasts ~0.6 of a whole tile.
-// item -> tile (mt, nt), first column n_off and width n_width inside the tile.
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int item, int& mt, int& nt, int& n_off,
-                                            int& n_width) {
-  int tile = item;
-  n_off = 0;
+//
+// Mixed widths (wide_tiles > 0, never together with slices): the channels of a row stripe are cut into
+// tiles_n tiles of which wide_tiles are 32 columns wider than the rest. The host picks tiles_n so that
+// tiles_m * tiles_n fills whole waves of the persistent grid when no single width does (M = 2048,
+// N = 7168 on 74 CTA pairs: 35 tiles of 192 and 2 of 224 per stripe are 296 tiles, exactly four per
+// pair, where 224-wide tiles alone need 3.46 waves). The wide tiles sit at the front of the stripe in
+// even raster groups and at its back in odd ones, so that they do not all land on the same workers.
+// item -> tile (mt, nt), n_start = first output column of the item, n_width = its accumulator columns,
+// alt = the item loads its weights through the second (slice / wide-tile) tensor map.
+__host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int item, int& mt, int& nt, int& n_start,
+                                                     int& n_width, bool& alt) {
+  int tile = item, n_off = 0;
   n_width = p.tile_n;
+  alt = false;
   if (item >= p.full_tiles) {
     const int extra = item - p.full_tiles;
     tile = p.full_tiles + extra / p.split;
     n_width = p.tile_n / p.split;
     n_off = (extra % p.split) * n_width;
+    alt = true;
   }
   const int per_group = p.group_m * p.tiles_n;
   const int group = tile / per_group;
   const int within = tile - group * per_group;
   const int first_m = group * p.group_m;
-  const int rows_in_group = min(p.group_m, p.tiles_m - first_m);
+  const int rows_left = p.tiles_m - first_m;
+  const int rows_in_group = p.group_m < rows_left ? p.group_m : rows_left;
   mt = first_m + within % rows_in_group;
   nt = within / rows_in_group;
+  if (p.wide_tiles > 0) {
+    const int narrow = p.tiles_n - p.wide_tiles;
+    // wide tiles before this one in the stripe
+    const int wide_before = (group & 1) ? (nt > narrow ? nt - narrow : 0) : (nt < p.wide_tiles ? nt : p.wide_tiles);
+    alt = (group & 1) ? nt >= narrow : nt < p.wide_tiles;
+    n_width = p.tile_n + (alt ? 32 : 0);
+    n_start = nt * p.tile_n + 32 * wide_before;
+  } else {
+    n_start = nt * p.tile_n + n_off;
+  }
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -174,12 +209,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 0 && lane == 0) {
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_w);
-    if (p.split > 1) prefetch_tensormap(&map_w_slice);
+    if (p.split > 1 || p.wide_tiles > 0 || (kMode == kModeBiased && kCtas == 2)) prefetch_tensormap(&map_w_slice);
     for (int d = 0; d < p.num_outputs; ++d) prefetch_tensormap(&out_maps.map[d]);
   }
   if constexpr (kMode == kModeBiased) {
-    // Sixteen rows of ones behind the 240 weight rows of every stage (the swizzle permutes
-    // 16-byte chunks within a row, so a constant fill is layout-independent).
+    if (kCtas == 1 || rank == 1) {
+    // Eight rows of ones behind the weight rows of every stage (the swizzle permutes 16-byte
+    // chunks within a row, so a constant fill is layout-independent).
     constexpr int kOnesBytes = Cfg::kOnesRows * Cfg::kBlockK;
     for (int i = threadIdx.x; i < Cfg::kStages * (kOnesBytes / 16); i += Cfg::kThreads) {
       const int s = i / (kOnesBytes / 16), c = i % (kOnesBytes / 16);
@@ -187,6 +223,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       reinterpret_cast<uint4*>(dst)[c] = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
     }
     fence_proxy_async_smem();
+  }
   }
   if (warp == 1) {
     tmem_alloc<kCtas>(smem_u32(tmem_slot), 512);
@@ -204,6 +241,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   // prefetch) may overlap the tail of the previous kernel in the stream; global memory is touched
   // only after that kernel has finished.
   pdl_wait();
+
+  // calls completed so far on this set of buffers (the rendezvous at the end counts from it)
+  const unsigned long long calls_done = out_maps.state ? ld_relaxed_u64(out_maps.state) : 0ull;
 
   const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;   // per group
   const int total_tiles = p.total_items;   // work items: whole tiles, then column slices
@@ -224,14 +264,17 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     const uint64_t a_policy = l2_policy_evict_last();
     bool ok = true;
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-      int mt, nt, n_off, n_width;
-      tile_coords(p, tile, mt, nt, n_off, n_width);
+      int mt, nt, n_start, n_width;
+      bool alt;
+      tile_coords(p, tile, mt, nt, n_start, n_width, alt);
       const int a_row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM;
-      // a pair's CTAs supply half the weight rows each; slices load through their own, narrower box
-      const int w_row = nt * p.tile_n + n_off + rank * (n_width / kCtas);
-      const bool slice = tile >= p.full_tiles;
-      const CUtensorMap* w_map = slice ? &map_w_slice : &map_w;
-      const uint32_t tx = static_cast<uint32_t>(slice ? p.stage_tx_slice : p.stage_tx) * kCtas;
+      // a pair's CTAs supply half the weight rows each; slices and wide tiles load through their own box
+      // (biased pair: the first CTA loads 128 channels through map_w, the second 120 through the other map)
+      const int w_row = n_start + rank * (kMode == kModeBiased ? Cfg::kBRowsSmem : n_width / kCtas);
+      const CUtensorMap* w_map = (alt || (kMode == kModeBiased && rank == 1)) ? &map_w_slice : &map_w;
+      const uint32_t tx = kMode == kModeBiased
+                              ? static_cast<uint32_t>(kCtas * Cfg::kABytes + Cfg::kChannelsPerTile * Cfg::kBlockK)
+                              : static_cast<uint32_t>(alt ? p.stage_tx_slice : p.stage_tx) * kCtas;
       for (int g = 0; ok && g < p.groups; ++g) {
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) { ok = false; break; }
@@ -263,8 +306,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       uint32_t phase = 0, acc_iter = 0;
       bool ok = true;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-        int mt, nt, n_off, n_width;
-        tile_coords(p, tile, mt, nt, n_off, n_width);
+        int mt, nt, n_start, n_width;
+        bool alt;
+        tile_coords(p, tile, mt, nt, n_start, n_width, alt);
         // accumulator columns the MMA produces (the biased form adds its 16 ones columns)
         const uint32_t idesc = idesc_i8(Cfg::kBlockM * kCtas, kMode == kModeBiased ? Cfg::kTileN : n_width,
                                         /*b_unsigned=*/kMode == kModeBiased);
@@ -322,23 +366,23 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     const uint64_t store_policy = l2_policy_evict_first();
     float total[kMode == kModeGrouped ? Cfg::kColsPerEpiWarp : 1];
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-      int mt, nt, n_off, n_width;
-      tile_coords(p, tile, mt, nt, n_off, n_width);
+      int mt, nt, n0, n_width;                            // n0 = first output column of this item
+      bool alt;
+      tile_coords(p, tile, mt, nt, n0, n_width, alt);
       const int row0 = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM + quarter * 32;
       const int row = row0 + lane;
-      const int n0 = nt * p.tile_n + n_off;               // first output column of this item
       for (int g = 0; g < p.groups; ++g, ++acc_iter) {
         const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
-        if (!mbar_wait<kCtas == 2>(tmem_full_bar(buf), acc_phase, abort_flag)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(tmem_full_bar(buf), acc_phase, abort_flag))) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                buf * Cfg::kTileN + col_base;
         const float row_scale = row < p.m ? p.sa[static_cast<size_t>(g) * p.m + row] : 0.f;
         int32_t bias = 0;
         if constexpr (kMode == kModeBiased) {
-          uint32_t ones[16];
-          tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                            buf * Cfg::kTileN + p.tile_n, ones);
+          uint32_t ones[8];
+          tmem_ld_32x8(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                           buf * Cfg::kTileN + p.tile_n, ones);
           tmem_ld_wait();
           bias = static_cast<int32_t>(ones[0]) * 128;
         }
@@ -485,6 +529,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
                 for (int j = 0; j < 16; j += 4)
                   *reinterpret_cast<uint4*>(dst + 2 * j) =
                       make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+              } else if (out_vec && limit % 8 == 0) {
+                // a tile edge inside these 32 columns (widths are multiples of 8): whole 16-byte groups
+#pragma unroll
+                for (int j = 0; j < 16; j += 4)
+                  if (2 * j < limit)
+                    *reinterpret_cast<uint4*>(dst + 2 * j) =
+                        make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
               } else {
                 for (int j = 0; j < 32; ++j)
                   if (j < limit) {
@@ -520,7 +571,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
     }
-    if (tma_out && lane == 0) tma_store_wait_read<0>();   // staged boxes must outlive their stores
+    if (tma_out && lane == 0) {
+      // staged boxes must outlive their stores; before the rendezvous the stores must have landed as well
+      if (out_maps.state) tma_store_wait_all(); else tma_store_wait_read<0>();
+    }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -533,6 +587,37 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 1) {
     tcgen05_fence_after();
     tmem_dealloc<kCtas>(tmem_base, 512);
+  }
+  if (out_maps.state != nullptr && threadIdx.x == 0) {
+    // Cross-GPU rendezvous. Every epilogue warp of this CTA has waited for its tile stores (the
+    // __syncthreads above orders that before this thread); the fences make those writes, which went
+    // through the async proxy, precede the release of the arrival counts at system scope.
+    fence_proxy_async_global();
+    __threadfence_system();
+    for (int d = 0; d < p.num_outputs; ++d) red_release_sys_add_u64(out_maps.signal[d] + out_maps.source, 1ull);
+    // one counter per source rank: a rank that is already a call ahead cannot stand in for a late one
+    const unsigned long long target = (calls_done + 1ull) * gridDim.x;
+    const unsigned long long start = global_timer_ns();
+    bool arrived = true;
+    for (int from = 0; arrived && from < p.num_outputs; ++from) {
+      for (uint32_t spin = 1; ld_acquire_sys_u64(out_maps.signal[0] + from) < target; ++spin) {
+        __nanosleep(64);
+        if ((spin & 255u) == 0u && global_timer_ns() - start > kWaitDeadlineNs) {
+          atomicOr(&g_ci8_status, kStatusPeerTimeout);   // a peer never arrived: the gathered result is incomplete
+          arrived = false;
+          break;
+        }
+      }
+    }
+    // the last CTA to leave publishes the call count for the next call on these buffers (after a
+    // timeout it still counts the call, so the host can read the status word and carry on)
+    (void)arrived;
+    __threadfence();
+    if (atomicAdd(out_maps.state + 1, 1ull) == gridDim.x - 1ull) {
+      out_maps.state[1] = 0ull;
+      __threadfence();
+      st_relaxed_u64(out_maps.state, calls_done + 1ull);
+    }
   }
 }
 

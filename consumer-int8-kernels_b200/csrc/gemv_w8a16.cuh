@@ -309,7 +309,8 @@ gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   int stage = 0;
   uint32_t phase = 0;
   for (int kb = 0; kb < num_kb; ++kb) {
-    if (!mbar_wait(full_bar(stage), phase, abort_flag)) break;
+    // the whole warp leaves together: ldmatrix and mma.sync below are warp-collective
+    if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag))) break;
     if (warp_active) {
       const uint32_t tile = smem_base + stage * Cfg::kStageBytes;
       const uint32_t x_tile = tile + Cfg::kWeightBytes;

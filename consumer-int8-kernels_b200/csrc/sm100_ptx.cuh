@@ -12,6 +12,7 @@ namespace ci8 {
 enum : unsigned {
   kStatusWaitTimeout = 1u,     // an mbarrier wait ran past its deadline
   kStatusClusterTimeout = 2u,  // a cluster-wide rendezvous ran past its deadline
+  kStatusPeerTimeout = 4u,     // the cross-GPU rendezvous of the gathering GEMM ran past its deadline
 };
 
 constexpr unsigned long long kWaitDeadlineNs = 2000000000ull;  // 2 s per wait
@@ -102,7 +103,9 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 
 // Bounded wait. Returns false when the wait was abandoned: either this waiter ran past the
 // deadline (it then raises *abort and the global status bit) or another role already aborted.
-template <bool kCluster = false>
+// kStatusBit is the bit raised on expiry: kStatusWaitTimeout for barriers fed inside the CTA (or its
+// pair), kStatusClusterTimeout for a barrier that another CTA of the cluster arrives on remotely.
+template <bool kCluster = false, unsigned kStatusBit = kStatusWaitTimeout>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort,
                                           unsigned long long deadline_ns = kWaitDeadlineNs) {
   if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
@@ -113,7 +116,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort) return false;
       if (global_timer_ns() - start > deadline_ns) {
         *abort = 1;
-        atomicOr(&g_ci8_status, kStatusWaitTimeout);
+        atomicOr(&g_ci8_status, kStatusBit);
         return false;
       }
     }
@@ -196,6 +199,35 @@ __device__ __forceinline__ void tma_store_commit() {
 template <int kPending>
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+
+// Waits until all of this thread's store groups have completed (their writes performed), not only
+// finished reading shared memory.
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+// Orders this thread's earlier async-proxy accesses to global memory (completed TMA stores) before
+// its later generic-proxy accesses.
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- system-scope counters (peer GPUs)
+__device__ __forceinline__ void red_release_sys_add_u64(unsigned long long* address, unsigned long long value) {
+  asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(address), "l"(value) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* address) {
+  unsigned long long value;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(value) : "l"(address) : "memory");
+  return value;
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* address) {
+  unsigned long long value;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(value) : "l"(address) : "memory");
+  return value;
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* address, unsigned long long value) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(address), "l"(value) : "memory");
 }
 
 // ---------------------------------------------------------------- cluster
@@ -320,6 +352,13 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&v)[16])
       : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
         "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
         "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&v)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
       : "r"(taddr)
       : "memory");
 }

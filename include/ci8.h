@@ -70,7 +70,10 @@ int ci8_cutlass_channel_mm(const int8_t* a, const int8_t* w, const float* a_scal
                            int k, ci8_stream_t stream);
 
 /* Replaces channel_mm (reference csrc/kernels.h:56-58, csrc/kernels.cu:299-303).
- * w UINT8 [n,k] holds signed code + 128. Any n > 0; k % 32 == 0, k <= 65536. */
+ * w UINT8 [n,k] holds signed code + 128. Any n > 0; k % 32 == 0, k <= 65536. a and w need 4-byte
+ * alignment only, as in the reference (it reads 32-bit words, csrc/kernels.cu:99,105); operands that
+ * are not 16-byte aligned run a plain word-wise kernel with the same bits, much slower than the
+ * tensor-core paths the aligned ones take. */
 int ci8_channel_mm(const int8_t* a, const uint8_t* w, const float* a_scale, const void* w_scale,
                    void* out, int m, int n, int k, ci8_stream_t stream);
 
@@ -153,10 +156,30 @@ int ci8_q8_block_static_max_values(void);
  * rank's [m, n_shard] result is written into block `rank` of every one of them with TMA tile
  * stores issued as each tile finishes, so the NVLink transfers overlap the main loop. The caller
  * must order a cross-rank barrier after this call before any rank reads its buffer.
- * w INT8 [n_shard, k] is this rank's slice of the weight; n_shard % 8 == 0; world <= 8. */
+ * w INT8 [n_shard, k] is this rank's slice of the weight; n_shard % 8 == 0; world <= 8. Of `schedule`
+ * only the choice between one-CTA (odd) and two-CTA (even) tiles is honoured: the tile width is
+ * chosen among those that are whole 64-column store boxes. */
 int ci8_fused_channel_mm_gather(const int8_t* a, const int8_t* w, const float* a_scale,
                                 const void* w_scale, void* const* gathered, int world, int rank,
                                 int m, int n_shard, int k, int schedule, ci8_stream_t stream);
+
+/* ci8_fused_channel_mm_gather with the closing cross-GPU barrier inside the kernel (no counterpart in
+ * the reference). signals[r] (a HOST array of device pointers, r = 0..world-1) points to 8 arrival
+ * counters of 8 bytes each in rank r's memory, peer-mapped into this process like the gathered
+ * buffers, zero before the first call and never reset; state points to 16 zero-initialised bytes in
+ * THIS rank's memory. Every CTA signals every rank after its stores have landed and then waits until
+ * all CTAs of all ranks have signalled this rank, so when the kernel ends the whole gathered result
+ * is in this rank's buffer: no collective has to follow. All ranks must make the same sequence of
+ * calls on one set of (gathered, signals, state). A rank may start call i+1 on a set while a peer
+ * still reads the result of call i from it, so alternate two sets when results are read between
+ * calls (call i+2 on a set cannot start before every rank has finished call i+1 on the other set,
+ * which orders it after every read of call i). A peer that never arrives ends the wait after 2 s
+ * with status bit 2 set (ci8_device_status); the call count still advances. Capturable in a CUDA
+ * graph: the call counter lives in `state`, not in the arguments. */
+int ci8_fused_channel_mm_gather_sync(const int8_t* a, const int8_t* w, const float* a_scale,
+                                     const void* w_scale, void* const* gathered, void* const* signals,
+                                     void* state, int world, int rank, int m, int n_shard, int k,
+                                     int schedule, ci8_stream_t stream);
 
 /* The streaming (m <= 64) kernel behind ci8_fused_channel_mm / ci8_cutlass_channel_mm /
  * ci8_channel_mm with the split-K factor forced to 1, 2 or 4 (1 or 2 for m > 16) instead of chosen
@@ -167,15 +190,29 @@ int ci8_decode_mm_split(const int8_t* a, const void* w, const float* a_scale, co
                         int32_t* workspace, void* out, int m, int n, int k, int split,
                         int weights_biased, ci8_stream_t stream);
 
+/* Diagnostic, no launch and no counterpart in the reference: the tiling ci8_fused_channel_mm (groups
+ * == 1, schedule 0) or ci8_grouped_channel_mm (groups > 1, k = 4096) would use for this shape on the
+ * current device. plan[0] = channels per tile, plan[1] = channel tiles per row stripe, plan[2] = how
+ * many of those are 32 channels wider than plan[0] (the mixed-width form), plan[3] = column slices
+ * the tiles of the last wave are cut into. Tests use it to make sure every form is exercised. */
+int ci8_gemm_tile_plan(int m, int n, int k, int groups, int* plan);
+
 /* Self-test of the kernels' bounded waits (no counterpart in the reference): launches one CTA that
  * waits on a barrier nothing arrives on; after deadline_us microseconds (1..1000000) the wait
  * gives up exactly as the production kernels' waits do after their 2 s deadline: status bit 0 is
  * raised, *gave_up (a device int) is set to 1 and the kernel returns, leaving the context usable. */
 int ci8_selftest_wait_timeout(unsigned deadline_us, int* gave_up, ci8_stream_t stream);
 
+/* The same for the rendezvous between the CTAs of a cluster (the split-K streaming kernel's leader
+ * waits for its peers' partial sums on a barrier they arrive on remotely): launches one 2-CTA cluster
+ * whose second CTA never arrives; after deadline_us the first CTA gives up, status bit 1 is raised,
+ * *gave_up is set to 1 and both CTAs leave through their closing cluster barrier. Nothing traps. */
+int ci8_selftest_cluster_timeout(unsigned deadline_us, int* gave_up, ci8_stream_t stream);
+
 /* Reads and clears the current device's kernel status word (synchronises the device). Bit 0: a
  * bounded wait inside a kernel ran past its deadline and the kernel gave up (its output is then
- * undefined). Returns 0 or a cudaError_t. Not for use during stream capture. */
+ * undefined); bit 1: a cluster rendezvous did; bit 2: the cross-GPU rendezvous of
+ * ci8_fused_channel_mm_gather_sync did (a peer never arrived). Returns 0 or a cudaError_t. Not for use during stream capture. */
 int ci8_device_status(unsigned* status);
 
 /* Text for a code returned by any function above. */

@@ -32,7 +32,7 @@ def test_library_exports_every_declared_symbol(ops):
     lib = ctypes.CDLL(str(ROOT / "consumer-int8-kernels_b200" / "consumer_int8" / "libci8.so"))
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in include/ci8.h but not exported"
-    assert lib.ci8_abi_version() == 1
+    assert lib.ci8_abi_version() == 2
     lib.ci8_error_string.restype = ctypes.c_char_p
     assert lib.ci8_error_string(0) == b"success"
     assert b"invalid" in lib.ci8_error_string(1).lower()
@@ -51,7 +51,7 @@ def test_arguments_are_rejected_before_any_launch(ops):
     assert lib.ci8_fused_channel_mm(one, one, one, one, one, 1, 4, 32, 7, null) == 1   # schedule
     assert lib.ci8_fused_channel_mm(one, one, one, one, one, 1, 4, 65568, 0, null) == 1  # k > 65536
     assert lib.ci8_channel_mm(one, one, one, one, one, 1, 4, 33, null) == 1
-    assert lib.ci8_channel_mm(ctypes.c_void_p(8), one, one, one, one, 1, 4, 32, null) == 1  # alignment
+    assert lib.ci8_channel_mm(ctypes.c_void_p(6), one, one, one, one, 1, 4, 32, null) == 1  # not even 4-byte aligned
     assert lib.ci8_channel_gemv(one, one, one, one, 17, 4, 32, null) == 1      # m > 16
     assert lib.ci8_channel_gemv(one, one, one, one, 1, 4, 24, null) == 1       # k % 16
     assert lib.ci8_cutlass_channel_mm(one, one, one, one, null, one, 1, 4, 32, null) == 1

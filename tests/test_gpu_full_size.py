@@ -49,6 +49,13 @@ def test_prefill_configs(ops, name, m, n, k):
     acc_rows = ref.int_mm_fast(want_codes[rows], inputs.w)
     assert_bit_equal(workspace[rows.to(DEV)], acc_rows, "sampled accumulators")
     del workspace
+    # the UINT8 code+128 form of the same weights (two-CTA biased tiles at this size)
+    other.fill_(float("nan"))
+    w_u8 = inputs.w_u8.to(DEV)
+    ops.channel_mm(codes, w_u8, scales, sw, other)
+    assert_bit_equal(other[rows.to(DEV)], want, "channel_mm sampled rows")
+    assert torch.equal(out, other), "channel_mm and fused_channel_mm differ"
+    del w_u8
     ops.fused_channel_mm(codes.neg(), w, scales, sw, other, 0)
     assert torch.equal(out.float(), -other.float()), "sign symmetry"
     perm = torch.randperm(m, device=DEV, generator=torch.Generator(device=DEV).manual_seed(2))

@@ -29,6 +29,24 @@ def test_grouped_channel_mm_matches_checker(ops, m, n, groups):
     assert device_status(ops) == 0
 
 
+def test_grouped_mixed_tile_widths_match_checker(ops):
+    """A shape whose automatic tiling mixes two tile widths (what the benchmark's M=2048, N=7168 does)."""
+    import ctypes
+
+    m, n, groups = 512, 14336, 2
+    plan = (ctypes.c_int * 4)()
+    assert ops.libci8.ci8_gemm_tile_plan(m, n, 4096, groups, plan) == 0
+    assert plan[2] > 0, f"this shape no longer exercises the mixed widths: {list(plan)}"
+    inputs = workloads.grouped_inputs(m, n, groups, seed=5)
+    codes, scales = ref.quantize_grouped4096_ref(inputs.x)
+    out, check = guarded((m, n), torch.bfloat16, float("nan"))
+    ops.grouped_channel_mm(codes.to(DEV), inputs.w.to(DEV), scales.to(DEV), inputs.w_scale.to(DEV), out)
+    want = ref.grouped_channel_mm_ref(codes, scales, inputs.w, inputs.w_scale, fast=True)
+    assert_bit_equal(out, want, "grouped out, mixed widths")
+    check()
+    assert device_status(ops) == 0
+
+
 def test_one_group_equals_fused_channel_mm(ops):
     inputs = workloads.grouped_inputs(200, 512, 1, seed=2)
     codes, scales = ref.quantize_grouped4096_ref(inputs.x)

@@ -111,8 +111,64 @@ def test_fused_channel_mm_tile_and_k_tails(ops, m, n, k, schedule):
     assert device_status(ops) == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(3, 37, 128), (70, 200, 256), (300, 520, 1024)])
+@pytest.mark.parametrize("shift_a,shift_w", [(4, 0), (0, 4), (8, 12)])
+def test_channel_mm_accepts_operands_that_are_only_four_byte_aligned(ops, m, n, k, shift_a, shift_w):
+    """The reference reads its operands as 32-bit words (csrc/kernels.cu:99,105) and checks no
+    alignment, so views at a 4-byte offset into a larger buffer must work here as well."""
+    a, w, sa, sw = linear_case(m, n, k, seed=m + n)
+    a_store = torch.zeros(m * k + 64, dtype=torch.int8, device=DEV)
+    w_store = torch.zeros(n * k + 64, dtype=torch.uint8, device=DEV)
+    da = a_store[shift_a:shift_a + m * k].view(m, k)
+    dw = w_store[shift_w:shift_w + n * k].view(n, k)
+    da.copy_(a)
+    dw.copy_(to_u8(w))
+    assert da.data_ptr() % 16 == shift_a % 16 and dw.data_ptr() % 16 == shift_w % 16
+    out, check = guarded((m, n), torch.bfloat16, float("nan"))
+    ops.channel_mm(da, dw, sa.to(DEV), sw.to(DEV), out)
+    _, want = ref.channel_mm_ref(a, to_u8(w), sa, sw)
+    assert_bit_equal(out, want, "channel_mm on 4-byte aligned views")
+    check()
+
+
+def _tile_plan(ops, m, n, k, groups=1):
+    plan = (ctypes.c_int * 4)()
+    assert ops.libci8.ci8_gemm_tile_plan(m, n, k, groups, plan) == 0
+    return dict(tile_n=plan[0], tiles_n=plan[1], wide_tiles=plan[2], split=plan[3])
+
+
+# Shapes whose automatic tiling mixes two tile widths (some channel tiles 32 columns wider than the
+# rest, so that the tiles fill whole waves); N tails and a ragged last unit included.
+MIXED_CASES = [(2048, 7168, 256), (2048, 7136, 160), (512, 14336, 256), (700, 14300, 96)]
+
+
+@pytest.mark.parametrize("m,n,k", MIXED_CASES)
+def test_mixed_tile_widths_match_checker(ops, m, n, k):
+    plan = _tile_plan(ops, m, n, k)
+    assert plan["wide_tiles"] > 0 and plan["split"] == 1, f"this shape no longer exercises the mixed widths: {plan}"
+    a, w, sa, sw = linear_case(m, n, k, seed=m + n + k)
+    da, dw, dsa, dsw = a.to(DEV), w.to(DEV), sa.to(DEV), sw.to(DEV)
+    out, check = guarded((m, n), torch.bfloat16, float("nan"))
+    ops.fused_channel_mm(da, dw, dsa, dsw, out, 0)
+    acc, want = ref.fused_channel_mm_ref(a, w, sa, sw, fast=True)
+    assert_bit_equal(out, want, f"fused, mixed widths {plan}")
+    check()
+    workspace, check_ws = guarded((m, n), torch.int32, -1)
+    out2, check2 = guarded((m, n), torch.bfloat16, float("nan"))
+    ops.cutlass_channel_mm(da, dw, dsa, dsw, workspace, out2)
+    assert_bit_equal(workspace, acc, "accumulators, mixed widths")
+    assert_bit_equal(out2, want, "workspace form, mixed widths")
+    check_ws()
+    check2()
+    assert device_status(ops) == 0
+
+
 @pytest.mark.parametrize("m,n,k", [(17, 37, 128), (128, 240, 128), (130, 241, 160), (300, 500, 1024),
-                                   (64, 5120, 5120), (1000, 1000, 992), (2048, 4096, 4096)])
+                                   (64, 5120, 5120), (1000, 1000, 992), (2048, 4096, 4096),
+                                   # edges of the 248-channel tile, one CTA (m <= 128) and a CTA pair, with and
+                                   # without an output pitch that allows TMA tile stores (n % 8)
+                                   (100, 248, 128), (128, 249, 160), (129, 248, 96), (257, 504, 256), (300, 2000, 96),
+                                   (513, 377, 64), (4096, 1000, 64), (256, 128, 32), (1300, 30000, 96)])
 def test_channel_mm_biased_weights_on_the_tensor_core_path(ops, m, n, k):
     a, w, sa, sw = linear_case(m, n, k, seed=3 * m + n)
     # extreme rows: the 128*sum(a) correction is largest when every activation is +-127
@@ -264,4 +320,30 @@ def test_a_wait_that_runs_out_sets_the_status_word_and_leaves_the_context_usable
     ops.fused_channel_mm(a.to(DEV), w.to(DEV), sa.to(DEV), sw.to(DEV), out)
     _, want = ref.fused_channel_mm_ref(a, w, sa, sw)
     assert_bit_equal(out, want, "GEMM after a timed-out wait")
+    assert device_status(ops) == 0
+
+
+def test_a_cluster_rendezvous_that_runs_out_sets_its_own_status_bit(ops):
+    """The split-K kernel's leader waits for its peers' partial sums on a barrier they arrive on from
+    another CTA. Here a two-CTA cluster runs in which the peer never arrives: the leader gives up
+    after 20 ms, status bit 1 (value 2) is raised, both CTAs leave, and a split-K product on the same
+    context right afterwards is bit-exact."""
+    assert device_status(ops) == 0
+    gave_up = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert ops.libci8.ci8_selftest_cluster_timeout(20000, ctypes.c_void_p(gave_up.data_ptr()), stream) == 0
+    torch.cuda.synchronize()
+    assert gave_up.item() == 1
+    assert device_status(ops) == 2          # bit 1: a rendezvous between CTAs ran past its deadline
+    assert device_status(ops) == 0
+    m, n, k = 8, 640, 2048
+    a, w, sa, sw = linear_case(m, n, k, seed=4)
+    _, want = ref.fused_channel_mm_ref(a, w, sa, sw)
+    for split in (2, 4):
+        out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+        da, dw, dsa, dsw = a.to(DEV), w.to(DEV), sa.to(DEV), sw.to(DEV)
+        rc = ops.libci8.ci8_decode_mm_split(*(ctypes.c_void_p(t.data_ptr()) for t in (da, dw, dsa, dsw)), ctypes.c_void_p(0),
+                                            ctypes.c_void_p(out.data_ptr()), m, n, k, split, 0, stream)
+        assert rc == 0
+        assert_bit_equal(out, want, f"split-K {split} after a timed-out rendezvous")
     assert device_status(ops) == 0
