@@ -10,6 +10,7 @@ GPU, the all-gather of the BF16 output). Workloads (shapes of the five benchmark
   sharded        M=16384 K=5120 N=34816, N split over the GPUs        (default, every --gpus)
   prefill_gate_up  M=4096 K=5120 N=34816       prefill_down   M=4096 K=17408 N=5120
   decode         M in {1,4,8,16} K=5120 N=34816 (HBM GB/s)            grouped  M=2048 K=8x4096 N=7168
+  peer_store     the sharded output with K=32: times the epilogue's (peer) tile stores alone
 
 ``value`` is whole-job throughput with inputs resident in HBM; ``e2e`` is the same metric through
 the public operators with host buffers (pinned host -> device copy of the activations and
@@ -45,6 +46,9 @@ WORKLOADS = {
     "grouped": dict(m=2048, k=32768, n=7168, groups=8, config="configs[3]"),
     "decode": dict(m=16, k=5120, n=34816, config="configs[1]"),
     "q8_block": dict(m=4096, k=4096, n=1024, config="block-32 Q8_0 (the reference's benchmark shape)"),
+    # the sharded output with next to no arithmetic (K = 32): what is left is the epilogue's tile stores,
+    # i.e. on several GPUs the peer-store bandwidth of the fused gather
+    "peer_store": dict(m=16384, k=32, n=34816, config="store-bandwidth probe of configs[4]'s output"),
 }
 METRIC = "W8A8 GEMM INT8 TOPS (quantize_rows + fused_channel_mm, whole job)"
 

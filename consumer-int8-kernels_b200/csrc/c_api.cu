@@ -956,6 +956,13 @@ int ci8_q8_block_mm(const void* x, int8_t* a, float* sa, const int8_t* w, const 
   return launch_q8_block(x, a, sa, w, sw, y, m, n, k, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// The reference's own name for this entry point (benchmarks/cuda/q8_block_int8.cu:150-160), so that its
+// validation script, which only accepts that name, can load this library unchanged.
+int q8_block_int8(const void* x, int8_t* a, float* sa, const int8_t* w, const void* sw, void* y, int m, int n, int k,
+                  ci8_stream_t stream) {
+  return ci8_q8_block_mm(x, a, sa, w, sw, y, m, n, k, stream);
+}
+
 int ci8_q8_block_mm_static(const void* x, const int8_t* w, const void* sw, void* y, int m, int n, int k,
                            ci8_stream_t stream) {
   if (!x || !w || !sw || !y || m <= 0 || n <= 0 || k <= 0 || k % 32 != 0 || k > 65536 ||

@@ -127,6 +127,12 @@ int ci8_gate_up_silu_mm(const int8_t* a, const int8_t* w, const float* a_scale, 
 int ci8_q8_block_mm(const void* x, int8_t* a, float* sa, const int8_t* w, const void* sw, void* y,
                     int m, int n, int k, ci8_stream_t stream);
 
+/* ci8_q8_block_mm under the reference's own symbol name (benchmarks/cuda/q8_block_int8.cu:150-160):
+ * the reference's validation script (benchmarks/benchmark_q8_block_int8.py:36-39,253-257) accepts no
+ * other entry name, so with this alias `--library libci8.so` is the only change to its command line. */
+int q8_block_int8(const void* x, int8_t* a, float* sa, const int8_t* w, const void* sw, void* y,
+                  int m, int n, int k, ci8_stream_t stream);
+
 /* ci8_q8_block_mm for callers that have no device memory to hand over. It has no counterpart in the
  * reference. ci8_q8_block_mm needs two caller-owned scratch buffers (the activation codes and their
  * block scales); some callers cannot provide them: a plugin that runs inside a serving engine whose

@@ -157,3 +157,16 @@ void ci8o_q8_block_mm(const int8_t* a, const int8_t* w, const float* sa, const u
       y[(int64_t)r * n + c] = f32_to_bf16(sum);
     }
 }
+
+/* Host twin of the reference's raw C entry point (benchmarks/cuda/q8_block_int8.cu:150-160, bound with
+ * ctypes at benchmarks/benchmark_q8_block_int8.py:36-39): same name, same argument order, HOST
+ * pointers, stream ignored. With it the reference's own validation script can be run against this
+ * checker on a machine without a GPU (tests/golden/run_reference_q8_validator.py). */
+int q8_block_int8(const void* x, void* a, void* sa, const void* w, const void* sw, void* y, int m, int n, int k,
+                  void* stream) {
+  (void)stream;
+  if (m <= 0 || n <= 0 || k <= 0 || k % 32) return 1;
+  ci8o_q8_block_quantize((const uint16_t*)x, (int8_t*)a, (float*)sa, (int64_t)m * (k / 32));
+  ci8o_q8_block_mm((const int8_t*)a, (const int8_t*)w, (const float*)sa, (const uint16_t*)sw, (uint16_t*)y, m, n, k);
+  return 0;
+}

@@ -23,7 +23,7 @@ SCHEMAS = {  # the reference's csrc/bindings.cpp:599,603-606,610
 def declared_symbols() -> list[str]:
     header = (ROOT / "include" / "ci8.h").read_text()
     header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
-    return re.findall(r"\b(ci8_[a-z0-9_]+)\s*\(", header)
+    return re.findall(r"\b((?:ci8_|q8_block_)[a-z0-9_]+)\s*\(", header)
 
 
 def test_library_exports_every_declared_symbol(ops):

@@ -11,6 +11,7 @@ import torch
 from oracle import w8a8_ref as ref
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
+ROOT = Path(__file__).resolve().parents[1]
 
 
 def sha(t: torch.Tensor) -> str:
@@ -219,3 +220,32 @@ def test_block32_checkers_agree_and_sit_inside_the_reference_tolerance(c_oracle,
     c_oracle.ci8o_q8_block_mm(ptr(codes), ptr(w), ptr(sa), ptr(sw), ptr(c_y), m, n, k)
     assert torch.equal(y.view(torch.int16), c_y.view(torch.int16))
     torch.testing.assert_close(y, ref.q8_block_mm_loose_ref(codes, w, sa, sw), rtol=0.008, atol=1e-5)
+
+
+def test_reference_block32_validator_passed_against_the_c_checker():
+    """The reference's own validation script for the block-32 path (benchmarks/benchmark_q8_block_int8.py)
+    was run, unmodified, against the C checker's host twin of its entry point; the record of that run is
+    a fixture. With CI8_REFERENCE_ROOT pointing at a checkout of the reference the run is repeated here
+    and must reproduce the record."""
+    import json
+    import os
+
+    record = json.loads((ROOT / "tests" / "golden" / "q8_block_validator.json").read_text())
+    assert record["passed"] is True and record["reference_script"] == "benchmarks/benchmark_q8_block_int8.py"
+    shapes = {(s["m"], s["n"], s["k"]): s for s in record["shapes"]}
+    assert set(shapes) == {(1, 1, 32), (17, 33, 96), (129, 65, 256)}      # the script's default shapes
+    for s in shapes.values():
+        assert s["entry"] == "q8_block_int8" and all(e < 0.015 for e in s["relative_l2"])
+    reference = os.environ.get("CI8_REFERENCE_ROOT")
+    if reference:
+        import importlib.util
+        import subprocess
+
+        subprocess.run(["make", "-s", "-C", str(ROOT / "oracle")], check=True)
+        spec = importlib.util.spec_from_file_location("run_reference_q8_validator",
+                                                      ROOT / "tests" / "golden" / "run_reference_q8_validator.py")
+        runner = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(runner)
+        again = runner.run(Path(reference), ROOT / "oracle" / "libci8_oracle.so")
+        assert again["reference_script_sha256"] == record["reference_script_sha256"]
+        assert again["shapes"] == record["shapes"]
