@@ -51,6 +51,7 @@ WORKLOADS = {
     "peer_store": dict(m=16384, k=32, n=34816, config="store-bandwidth probe of configs[4]'s output"),
 }
 METRIC = "W8A8 GEMM INT8 TOPS (quantize_rows + fused_channel_mm, whole job)"
+RESULT_STREAM = sys.stdout     # main() replaces it by the original stdout and points fd 1 at stderr
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -198,7 +199,7 @@ def run_reference(args, spec, rank):
                             step=("the whole workload per step on the host CPU" if rows == spec["m"] else
                                   f"{rows}-row sample per step on the host CPU")),
                 cpu_baseline=sample, e2e=dict(value=tops, unit="TOPS", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=RESULT_STREAM, flush=True)
 
 
 # ----------------------------------------------------------------------------- GPU arm
@@ -243,7 +244,7 @@ def run_ours(args, spec, rank, world, local_rank):
     x_host = workloads.activations(m, k, gen).pin_memory()
     w, w_scale = workloads.weights(n, k, gen)
     mode = args.gather if world > 1 else "nccl"
-    fused = mode in ("fused", "fused_nccl_barrier")
+    fused = mode in ("fused", "fused_flag", "fused_nccl_barrier")
     plan = ShardPlan(m, n, k, world, rank, chunks=args.chunks if mode == "nccl" and world > 1 else 1)
     w_shard, sw_shard = plan.shard_weights(w, w_scale)
     layer = ColumnShardedLinear(plan, w_shard.to(device), sw_shard.to(device), schedule=args.schedule, mode=mode)
@@ -388,6 +389,7 @@ def run_ours(args, spec, rank, world, local_rank):
                     gather=("none" if world == 1 else
                             "fused: GEMM epilogue TMA-stores each tile into every rank's symmetric-memory buffer, closed by "
                             "an in-kernel rendezvous" if mode == "fused" else
+                            "fused stores closed by a one-thread rendezvous kernel" if mode == "fused_flag" else
                             "fused stores closed by an NCCL barrier" if mode == "fused_nccl_barrier" else
                             "NCCL all-gather of BF16 [M,N/G] blocks"),
                     row_chunks=plan.chunks, schedule=args.schedule,
@@ -415,7 +417,7 @@ def run_ours(args, spec, rank, world, local_rank):
         line["cpu_baseline"] = sample
         if not args.no_extra:
             line["other_configs"] = other_configs(ops, workloads, device, peaks)
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=RESULT_STREAM, flush=True)
 
 
 # DRAM bytes per launch of the dominant kernel from ncu captures (dram__bytes_read.sum and
@@ -595,9 +597,18 @@ def other_configs(ops, workloads, device, peaks):
     scales = torch.empty(groups, m, device=device)
     out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
     ms_q = _time_graph(lambda i: ops.quantize_grouped4096(xs[i % 2], codes, scales), 20)
-    ms = _time_graph(lambda i: ops.grouped_channel_mm(codes, wd, scales, sw, out), 10)
+    ms_plain = _time_graph(lambda i: ops.grouped_channel_mm(codes, wd, scales, sw, out), 10)
+    # with a lent workspace the tiles of the thin last wave are split along the groups (same bits)
+    need = ops.grouped_workspace_bytes(m, n, groups)
+    ms = ms_plain
+    if need:
+        workspace = torch.zeros(need, dtype=torch.uint8, device=device)
+        ms_ws = _time_graph(lambda i: ops.grouped_channel_mm_ws(codes, wd, scales, sw, workspace, out), 10)
+        ms = ms_ws if ms_ws < ms_plain else ms_plain
     tops = 2.0 * m * n * groups * 4096 / ms / 1e9
-    results["grouped"] = dict(gemm_ms=ms, gemm_ms_min_max=[ms.lo, ms.hi], tops=tops, frac_tensor=tops / tensor_peak,
+    results["grouped"] = dict(gemm_ms=ms, gemm_ms_min_max=[ms.lo, ms.hi], plain_ms=ms_plain,
+                              with_workspace_ms=ms_ws if need else None, workspace_bytes=need,
+                              tops=tops, frac_tensor=tops / tensor_peak,
                               frac_tensor_sustained=tops / (2.0 * peaks["bf16_tflops_sustained"]), frac_nominal_4500=tops / 4500,
                               quantize_us=ms_q * 1e3, quantize_us_min_max=_spread_us(ms_q),
                               quantize_gbs=(3 * m * groups * 4096 + 4 * m * groups) / ms_q / 1e6,
@@ -651,9 +662,10 @@ def profile_only(args, spec):
         codes = torch.empty(spec["groups"], m, 4096, dtype=torch.int8, device=device)
         scales = torch.empty(spec["groups"], m, device=device)
         out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+        workspace = torch.zeros(max(ops.grouped_workspace_bytes(m, n, spec["groups"]), 16), dtype=torch.uint8, device=device)
         for _ in range(args.steps):
             ops.quantize_grouped4096(x, codes, scales)
-            ops.grouped_channel_mm(codes, w, scales, sw, out)
+            ops.grouped_channel_mm_ws(codes, w, scales, sw, workspace, out)
     else:
         inputs = workloads.linear_inputs(m, n, k, seed=0)
         x, sw = inputs.x.to(device), inputs.w_scale.to(device)
@@ -668,7 +680,16 @@ def profile_only(args, spec):
                 ops.channel_gemv(x, copies[i % len(copies)], sw, out)
                 ops.dynamic_channel_mm(x, copies[i % len(copies)], sw, codes, scales, out)
     torch.cuda.synchronize()
-    print(json.dumps(dict(profile_only=args.workload, launches=args.steps)), flush=True)
+    print(json.dumps(dict(profile_only=args.workload, launches=args.steps)), file=RESULT_STREAM, flush=True)
+
+
+def _claim_stdout():
+    """Keeps stdout for the one JSON line: everything else that writes to file descriptor 1 (a library's
+    version banner, for one) goes to stderr. Returns a file object on the original stdout."""
+    sys.stdout.flush()
+    kept = os.dup(1)
+    os.dup2(2, 1)
+    return os.fdopen(kept, "w")
 
 
 def main():
@@ -681,7 +702,7 @@ def main():
     parser.add_argument("--profile-only", action="store_true",
                         help="run --steps launches of the workload's kernels with no timing (for ncu captures)")
     parser.add_argument("--schedule", type=int, default=0)
-    parser.add_argument("--gather", choices=["fused", "fused_nccl_barrier", "nccl"], default="fused",
+    parser.add_argument("--gather", choices=["fused", "fused_flag", "fused_nccl_barrier", "nccl"], default="fused",
                         help="N>1: peer stores from the GEMM epilogue (closed inside the kernel, or by an NCCL "
                              "barrier), or a separate NCCL all-gather")
     parser.add_argument("--chunks", type=int, default=4,
@@ -692,6 +713,8 @@ def main():
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    global RESULT_STREAM
+    RESULT_STREAM = _claim_stdout()
     if args.impl == "reference":
         run_reference(args, spec, rank)
         return

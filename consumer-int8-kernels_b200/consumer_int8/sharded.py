@@ -15,8 +15,10 @@ Ways to move it (``mode``):
   buffer is complete, and no collective follows. The layer owns TWO sets of buffers and alternates
   between them, so a rank that is already in its next call never writes into a result that a peer
   is still reading: the tensor ``forward`` returns stays valid until the second-next ``forward``.
+* ``"fused_flag"``: the same stores; the GEMM kernel ends as soon as its own work is done and a
+  one-thread kernel behind it (``ops.peer_rendezvous``) exchanges the arrival counts.
 * ``"fused_nccl_barrier"``: the same stores, closed by a small stream-ordered NCCL all-reduce instead
-  of the in-kernel rendezvous (the first form of this path; kept for comparison).
+  (the first form of this path; kept for comparison).
 * ``"nccl"``: the GEMM writes its block locally and one NCCL all-gather moves it.
 * ``"none"``: no gather at all: the result stays column-sharded, ``[M, N/G]`` per rank in block ``rank``
   of the returned buffer. A row-parallel layer that follows (the down projection after a column-
@@ -93,7 +95,8 @@ class ShardPlan:
         return gathered.permute(0, 2, 1, 3).reshape(self.m, self.n)
 
 
-MODES = ("fused", "fused_nccl_barrier", "nccl", "none")
+MODES = ("fused", "fused_flag", "fused_nccl_barrier", "nccl", "none")
+FUSED_MODES = ("fused", "fused_flag", "fused_nccl_barrier")
 
 
 class ColumnShardedLinear:
@@ -127,7 +130,7 @@ class ColumnShardedLinear:
         self.mode = mode if plan.world > 1 else "nccl"
         self.calls = 0
         self._sets = []            # fused modes: two sets of (gathered, peer_ptrs, signal_ptrs, state, handles)
-        if self.mode in ("fused", "fused_nccl_barrier"):
+        if self.mode in FUSED_MODES:
             if plan.chunks != 1:
                 raise ValueError("the fused gather overlaps tile by tile; use chunks=1")
             if plan.shard_n % 8:
@@ -176,7 +179,7 @@ class ColumnShardedLinear:
             self.compute(x)
             return self.gathered
         self.ops.quantize_rows(x, self.codes, self.scales)
-        if self.mode in ("fused", "fused_nccl_barrier"):
+        if self.mode in FUSED_MODES:
             # every rank writes its block into every rank's buffer; the two sets alternate so that a
             # rank already in its next call cannot overwrite a result a peer still reads
             current = self._sets[self.calls % 2]
@@ -189,7 +192,10 @@ class ColumnShardedLinear:
             else:
                 self.ops.fused_channel_mm_gather(self.codes, self.w, self.scales, self.w_scale, self.gathered[0],
                                                  current["peer_ptrs"], plan.rank, self.schedule)
-                dist.all_reduce(self._barrier_word, group=self.group)   # stream-ordered, no host sync
+                if self.mode == "fused_flag":
+                    self.ops.peer_rendezvous(current["signal_ptrs"], current["state"], plan.rank)
+                else:
+                    dist.all_reduce(self._barrier_word, group=self.group)   # stream-ordered, no host sync
             return self.gathered
         main = torch.cuda.current_stream() if self.comm_stream is not None else None
         for c in range(plan.chunks):

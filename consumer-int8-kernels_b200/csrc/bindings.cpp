@@ -221,9 +221,11 @@ void boxed_fused_mm(StableIValue* stack, uint64_t, uint64_t) { tiled_mm_impl(sta
 
 // Additive operator (no counterpart in the reference's surface): the grouped-scale GEMM in one
 // launch, consuming what quantize_grouped4096 writes.
-void boxed_grouped_mm(StableIValue* stack, uint64_t, uint64_t) {
+// The _ws form takes a caller-lent BYTE workspace (zero before its first use) in front of `out`; with
+// at least ci8_grouped_workspace_bytes() of it the tiles of a thin last wave are split along the groups.
+void grouped_mm_impl(StableIValue* stack, bool with_workspace) {
   auto codes = to<Tensor>(stack[0]), w = to<Tensor>(stack[1]), scales = to<Tensor>(stack[2]);
-  auto sw = to<Tensor>(stack[3]), out = to<Tensor>(stack[4]);
+  auto sw = to<Tensor>(stack[3]), out = to<Tensor>(stack[with_workspace ? 5 : 4]);
   const int device = codes.get_device_index();
   check(codes, ScalarType::Char, device);
   check(w, ScalarType::Char, device);
@@ -240,11 +242,22 @@ void boxed_grouped_mm(StableIValue* stack, uint64_t, uint64_t) {
                   "Invalid grouped GEMM geometry");
   STD_TORCH_CHECK(codes.numel() <= kIntMax && w.numel() <= kIntMax && out.numel() <= kIntMax, "Matrix too large");
   STD_TORCH_CHECK(address(codes) % 16 == 0 && address(w) % 16 == 0, "Matrix operands must be 16-byte aligned");
+  void* workspace = nullptr;
+  long long workspace_bytes = 0;
+  if (with_workspace) {
+    auto lent = to<Tensor>(stack[4]);
+    check(lent, ScalarType::Byte, device);
+    STD_TORCH_CHECK(address(lent) % 16 == 0, "The workspace must be 16-byte aligned");
+    workspace = lent.data_ptr();
+    workspace_bytes = lent.numel();
+  }
   torch::stable::accelerator::DeviceGuard guard(device);
-  launched(ci8_grouped_channel_mm(static_cast<int8_t*>(codes.data_ptr()), static_cast<int8_t*>(w.data_ptr()),
-                                  static_cast<float*>(scales.data_ptr()), sw.data_ptr(), out.data_ptr(), m, n,
-                                  groups, stream_for(device)));
+  launched(ci8_grouped_channel_mm_ws(static_cast<int8_t*>(codes.data_ptr()), static_cast<int8_t*>(w.data_ptr()),
+                                     static_cast<float*>(scales.data_ptr()), sw.data_ptr(), out.data_ptr(), workspace,
+                                     workspace_bytes, m, n, groups, stream_for(device)));
 }
+void boxed_grouped_mm(StableIValue* stack, uint64_t, uint64_t) { grouped_mm_impl(stack, false); }
+void boxed_grouped_mm_ws(StableIValue* stack, uint64_t, uint64_t) { grouped_mm_impl(stack, true); }
 
 // Additive operator: quantize_rows + fused_channel_mm as one call (one kernel for decode shapes); codes and
 // scales receive what quantize_rows would write.
@@ -358,6 +371,26 @@ void gather_common(StableIValue* stack, bool sync) {
                                             state.data_ptr(), static_cast<int>(world), static_cast<int>(rank), m, n, k,
                                             static_cast<int>(schedule), stream_for(device)));
 }
+// peer_rendezvous(signal_ptrs CPU INT64[world], state INT64[2] on this device, rank): the closing barrier
+// of fused_channel_mm_gather as a kernel of its own.
+void boxed_peer_rendezvous(StableIValue* stack, uint64_t, uint64_t) {
+  auto signal_ptrs = to<Tensor>(stack[0]), state = to<Tensor>(stack[1]);
+  const int64_t rank = to<int64_t>(stack[2]);
+  const int device = state.get_device_index();
+  check(state, ScalarType::Long, device);
+  STD_TORCH_CHECK(state.numel() == 2, "state must hold two INT64 words");
+  STD_TORCH_CHECK(!signal_ptrs.is_cuda() && signal_ptrs.is_contiguous() && signal_ptrs.scalar_type() == ScalarType::Long &&
+                      signal_ptrs.dim() == 1 && signal_ptrs.size(0) > 0 && signal_ptrs.size(0) <= 8,
+                  "signal_ptrs must be a contiguous CPU INT64 vector with one entry per rank");
+  const int64_t world = signal_ptrs.size(0);
+  STD_TORCH_CHECK(rank >= 0 && rank < world, "rank outside the world");
+  const int64_t* addresses = static_cast<const int64_t*>(signal_ptrs.data_ptr());
+  void* signals[8];
+  for (int64_t r = 0; r < world; ++r) signals[r] = reinterpret_cast<void*>(static_cast<uintptr_t>(addresses[r]));
+  torch::stable::accelerator::DeviceGuard guard(device);
+  launched(ci8_peer_rendezvous(signals, state.data_ptr(), static_cast<int>(world), static_cast<int>(rank),
+                               stream_for(device)));
+}
 void boxed_fused_mm_gather(StableIValue* stack, uint64_t, uint64_t) { gather_common(stack, false); }
 void boxed_fused_mm_gather_sync(StableIValue* stack, uint64_t, uint64_t) { gather_common(stack, true); }
 }  // namespace
@@ -373,9 +406,11 @@ STABLE_TORCH_LIBRARY(consumer_int8, m) {
   m.def("channel_gemv(Tensor x, Tensor w, Tensor scale, Tensor(a!) out) -> ()");
   m.def("cutlass_channel_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) workspace, Tensor(b!) out) -> ()");
   m.def("grouped_channel_mm(Tensor codes, Tensor w, Tensor scales, Tensor w_scale, Tensor(a!) out) -> ()");
+  m.def("grouped_channel_mm_ws(Tensor codes, Tensor w, Tensor scales, Tensor w_scale, Tensor(a!) workspace, Tensor(b!) out) -> ()");
   m.def("dynamic_channel_mm(Tensor x, Tensor w, Tensor w_scale, Tensor(a!) codes, Tensor(b!) scales, Tensor(c!) out) -> ()");
   m.def("gate_up_silu_mm(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) out) -> ()");
   m.def("fused_channel_mm_gather(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) gathered, Tensor peer_ptrs, int rank, int schedule=0) -> ()");
+  m.def("peer_rendezvous(Tensor signal_ptrs, Tensor(a!) state, int rank) -> ()");
   m.def("fused_channel_mm_gather_sync(Tensor a, Tensor w, Tensor a_scale, Tensor w_scale, Tensor(a!) gathered, Tensor peer_ptrs, Tensor signal_ptrs, Tensor(b!) state, int rank, int schedule=0) -> ()");
 }
 STABLE_TORCH_LIBRARY_IMPL(consumer_int8, CUDA, m) {
@@ -389,10 +424,12 @@ STABLE_TORCH_LIBRARY_IMPL(consumer_int8, CUDA, m) {
   m.impl("channel_gemv", &boxed_gemv);
   m.impl("cutlass_channel_mm", &boxed_cutlass_mm);
   m.impl("grouped_channel_mm", &boxed_grouped_mm);
+  m.impl("grouped_channel_mm_ws", &boxed_grouped_mm_ws);
   m.impl("gate_up_silu_mm", &boxed_gate_up_silu_mm);
   m.impl("dynamic_channel_mm", &boxed_dynamic_mm);
   m.impl("fused_channel_mm_gather", &boxed_fused_mm_gather);
   m.impl("fused_channel_mm_gather_sync", &boxed_fused_mm_gather_sync);
+  m.impl("peer_rendezvous", &boxed_peer_rendezvous);
 }
 extern "C" PyObject* PyInit__C() {
   static PyModuleDef module = {PyModuleDef_HEAD_INIT, "_C", nullptr, -1, nullptr};

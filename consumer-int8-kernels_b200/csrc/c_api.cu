@@ -8,6 +8,7 @@
 
 #include <atomic>
 #include <cstdint>
+#include <cstdlib>
 
 #include "allspark_unpack.cuh"
 #include "decode_splitk.cuh"
@@ -112,6 +113,29 @@ cudaError_t make_bf16_map(CUtensorMap* map, const void* base, uint64_t rows, uin
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// Bytes of activations one raster group may hold (they are meant to stay in L2 while the weights stream
+// past). CI8_RASTER_MIB overrides the default for experiments; read once.
+long long raster_bytes() {
+  static const long long bytes = [] {
+    const char* text = std::getenv("CI8_RASTER_MIB");
+    const long mib = text ? std::strtol(text, nullptr, 10) : 0;
+    return static_cast<long long>(mib >= 1 && mib <= 120 ? mib : 36) << 20;
+  }();
+  return bytes;
+}
+
+// Grouped form with a workspace: how many tiles (256 x 256, CTA pairs) the last, partial wave holds when
+// cutting them along the groups pays: one piece per worker at most, and a last wave less than half
+// full (a fuller one is better left alone). 0 otherwise.
+constexpr size_t kPieceHeaderBytes = 1024;                       // the pieces' counters
+constexpr size_t kPieceTermBytes = 256 * 256 * sizeof(float);    // one group's terms of one tile
+int grouped_leftover_tiles(int m, int n, int groups, long long workers) {
+  if (m <= 128 || groups < 2) return 0;
+  const long long tiles = static_cast<long long>((m + 255) / 256) * ((n + 255) / 256);
+  const long long rest = tiles % workers;
+  return (rest > 0 && rest * groups <= workers && 2 * rest <= workers) ? static_cast<int>(rest) : 0;
+}
+
 // Fills the tiling of a launch into p (tiles_m, group_m, tile_n, tiles_n, wide_tiles, split, full_tiles,
 // total_items, out_n) for `workers` persistent CTAs (CTA pairs for kCtas == 2). p.tile_n > 0 on entry
 // forces that width (a schedule); num_outputs > 1 is the gathering form.
@@ -161,10 +185,13 @@ void plan_tiles(GemmParams& p, int num_outputs, long long workers) {
   // problems of a few waves (beyond that a partial last wave is noise, and the walk would cost time).
   int mixed_count = 0, mixed_base = 0, mixed_wide = 0;
   // rows of A per raster group: about 32 MiB of activations, so they stay in L2
-  const long long group_rows = (32ll << 20) / (static_cast<long long>(p.k) * p.groups);
-  p.group_m = static_cast<int>(group_rows / (Cfg::kBlockM * kCtas));
-  if (p.group_m < 1) p.group_m = 1;
-  if (p.group_m > p.tiles_m) p.group_m = p.tiles_m;
+  // (every raster group streams the whole of W once, so the groups are made equal: 16 row tiles under a cap
+  // of 7 become two groups of 8, not 7 + 7 + 2)
+  const long long group_rows = raster_bytes() / (static_cast<long long>(p.k) * p.groups);
+  int cap_m = static_cast<int>(group_rows / (Cfg::kBlockM * kCtas));
+  if (cap_m < 1) cap_m = 1;
+  const int raster_groups = (p.tiles_m + cap_m - 1) / cap_m;
+  p.group_m = (p.tiles_m + raster_groups - 1) / raster_groups;
   if ((kMode == kModeFused || kMode == kModeWorkspace || kMode == kModeGrouped) && num_outputs <= 1 && !forced &&
       workers <= 256) {
     // the decision depends on the shape only: remember the last one per thread
@@ -205,6 +232,16 @@ void plan_tiles(GemmParams& p, int num_outputs, long long workers) {
     split = 1;
     p.wide_tiles = mixed_wide;
   }
+  // Fourth remedy, grouped form only, when the caller has lent a workspace (p.terms): 256-wide tiles, the
+  // leftover tiles cut along the groups into pieces that all run at once.
+  const int leftover = (kMode == kModeGrouped && kCtas == 2 && p.terms) ? grouped_leftover_tiles(p.m, p.n, p.groups, workers) : 0;
+  p.piece_items = 0;
+  if (leftover > 0) {
+    tile_n = 256;
+    split = 1;
+    p.wide_tiles = 0;
+    mixed_count = 0;
+  }
   p.tile_n = tile_n;
   p.tiles_n = mixed_count > 0 ? mixed_count : (p.n + tile_n - 1) / tile_n;
   {
@@ -212,6 +249,11 @@ void plan_tiles(GemmParams& p, int num_outputs, long long workers) {
     p.split = split;
     p.full_tiles = split > 1 ? static_cast<int>(tiles - tiles % workers) : static_cast<int>(tiles);
     p.total_items = p.full_tiles + static_cast<int>(tiles - p.full_tiles) * split;
+    if (leftover > 0) {
+      p.full_tiles = static_cast<int>(tiles - leftover);
+      p.piece_items = leftover * p.groups;
+      p.total_items = p.full_tiles + p.piece_items;
+    }
   }
 }
 
@@ -455,8 +497,10 @@ void launch_quantize_vec(const void* x, int8_t* q, float* s, int rows, int k, in
   }
   const int needed = (rows + kRowsPerCta - 1) / kRowsPerCta;
   constexpr bool kPersistent = !kSwiGLU && kPacks >= 4 && kPacks <= 9;
-  launch_serialized(quantize_rows_vec_kernel<kTeam, kPacks, kSwiGLU>,
-                    static_cast<unsigned>((!kPersistent || needed < per_device) ? needed : per_device), kThreads, 0,
+  // (making every CTA of the persistent form walk the same number of rows, 512 CTAs x 4 passes instead of
+  // 592 CTAs x 3.46, was measured 20-25 % SLOWER: the kernel lives on the number of loads in flight)
+  const int grid = (!kPersistent || needed < per_device) ? needed : per_device;
+  launch_serialized(quantize_rows_vec_kernel<kTeam, kPacks, kSwiGLU>, static_cast<unsigned>(grid), kThreads, 0,
                     stream, static_cast<const uint16_t*>(x), q, s, rows, k, m, groups);
 }
 
@@ -613,6 +657,36 @@ __global__ void __cluster_dims__(2, 1, 1) cluster_timeout_selftest_kernel(unsign
   }
   cluster_arrive();
   cluster_wait();
+}
+
+// Cross-GPU rendezvous as a kernel of its own (one thread): everything this GPU's earlier kernels in the
+// stream wrote into its peers' memory is complete when this kernel starts; it tells every peer so
+// (one arrival counter per source rank in each peer's memory) and waits until every peer has told it
+// the same. The call counter lives in `state`, so the kernel can be replayed from a CUDA graph.
+struct RendezvousParams {
+  unsigned long long* signal[ci8::kMaxOutputs];   // signal[r]: rank r's counters (peer-mapped); [rank] is this GPU's own
+  unsigned long long* state;
+  int world, rank;
+};
+__global__ void peer_rendezvous_kernel(const RendezvousParams p) {
+  if (threadIdx.x != 0) return;
+  const unsigned long long calls_done = ld_relaxed_u64(p.state);
+  __threadfence_system();
+  for (int d = 1; d < p.world; ++d) red_release_sys_add_u64(p.signal[(p.rank + d) % p.world] + p.rank, 1ull);
+  const unsigned long long start = global_timer_ns();
+  for (int from = 0; from < p.world; ++from) {
+    if (from == p.rank) continue;
+    for (uint32_t spin = 1; ld_acquire_sys_u64(p.signal[p.rank] + from) < calls_done + 1ull; ++spin) {
+      __nanosleep(32);
+      if ((spin & 255u) == 0u && global_timer_ns() - start > kWaitDeadlineNs) {
+        atomicOr(&g_ci8_status, kStatusPeerTimeout);
+        from = p.world;
+        break;
+      }
+    }
+  }
+  __threadfence();
+  st_relaxed_u64(p.state, calls_done + 1ull);
 }
 
 }  // namespace
@@ -803,8 +877,8 @@ int ci8_channel_gemv(const void* x, const int8_t* w, const void* w_scale, void* 
   if (aligned(x, 16) && n >= 2048) {
     // production path: TMA-staged weights, one CTA per slab of channels, one wave
     const int sms = sm_count();
-    int slab = ((n + sms - 1) / sms + 31) / 32 * 32;
-    if (slab < 32) slab = 32;
+    int slab = ((n + sms - 1) / sms + 15) / 16 * 16;   // a consumer warp owns 16 channels
+    if (slab < 16) slab = 16;
     if (slab > GemvTmaConfig::kMaxSlab) slab = GemvTmaConfig::kMaxSlab;
     static std::atomic<uint64_t> smem_done1{0}, smem_done2{0};
     cudaError_t err = m <= 8 ? ensure_smem(gemv_w8a16_tma_kernel<1>, GemvTmaConfig::kSmemBytes, smem_done1)
@@ -843,16 +917,35 @@ int ci8_channel_gemv(const void* x, const int8_t* w, const void* w_scale, void* 
   return launch_gemv<16>(x, w, w_scale, out, m, n, k, s);
 }
 
-int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* scales, const void* w_scale,
-                           void* out, int m, int n, int groups, ci8_stream_t stream) {
+long long ci8_grouped_workspace_bytes(int m, int n, int groups) {
+  if (m <= 0 || n <= 0 || groups <= 0 || groups > 16) return 0;
+  const int leftover = grouped_leftover_tiles(m, n, groups, sm_count() / 2);
+  return leftover > 0 ? static_cast<long long>(kPieceHeaderBytes + static_cast<size_t>(leftover) * groups * kPieceTermBytes) : 0;
+}
+
+int ci8_grouped_channel_mm_ws(const int8_t* codes, const int8_t* w, const float* scales, const void* w_scale,
+                              void* out, void* workspace, long long workspace_bytes, int m, int n, int groups,
+                              ci8_stream_t stream) {
   if (!codes || !w || !scales || !w_scale || !out || m <= 0 || n <= 0 || groups <= 0 || groups > 16 ||
       static_cast<long long>(m) * groups * 4096 > INT32_MAX || static_cast<long long>(n) * groups * 4096 > INT32_MAX ||
-      static_cast<long long>(m) * n > INT32_MAX || !aligned(codes, 16) || !aligned(w, 16))
+      static_cast<long long>(m) * n > INT32_MAX || !aligned(codes, 16) || !aligned(w, 16) || workspace_bytes < 0 ||
+      (workspace && !aligned(workspace, 16)))
     return kInvalid;
   GemmParams p{scales, static_cast<const __nv_bfloat16*>(w_scale), static_cast<__nv_bfloat16*>(out), nullptr,
                m, n, 4096, groups, 0, 0, 0, 0, 0, 0};
+  // a workspace that is large enough switches on the split of the last wave's tiles along the groups
+  const long long needed = ci8_grouped_workspace_bytes(m, n, groups);
+  if (workspace && needed > 0 && workspace_bytes >= needed) {
+    p.piece_sync = static_cast<unsigned*>(workspace);
+    p.terms = reinterpret_cast<float*>(static_cast<char*>(workspace) + kPieceHeaderBytes);
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return m > 128 ? launch_gemm<2, kModeGrouped>(codes, w, p, s) : launch_gemm<1, kModeGrouped>(codes, w, p, s);
+}
+
+int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* scales, const void* w_scale,
+                           void* out, int m, int n, int groups, ci8_stream_t stream) {
+  return ci8_grouped_channel_mm_ws(codes, w, scales, w_scale, out, nullptr, 0, m, n, groups, stream);
 }
 
 namespace {
@@ -897,6 +990,21 @@ int ci8_fused_channel_mm_gather_sync(const int8_t* a, const int8_t* w, const flo
                                      int m, int n_shard, int k, int schedule, ci8_stream_t stream) {
   if (!signals || !state || !aligned(state, 8)) return kInvalid;
   return gather_impl(a, w, a_scale, w_scale, gathered, signals, state, world, rank, m, n_shard, k, schedule, stream);
+}
+
+int ci8_peer_rendezvous(void* const* signals, void* state, int world, int rank, ci8_stream_t stream) {
+  if (!signals || !state || !aligned(state, 8) || world <= 0 || world > kMaxOutputs || rank < 0 || rank >= world)
+    return kInvalid;
+  RendezvousParams p = {};
+  for (int r = 0; r < world; ++r) {
+    if (!signals[r] || !aligned(signals[r], 8)) return kInvalid;
+    p.signal[r] = static_cast<unsigned long long*>(signals[r]);
+  }
+  p.state = static_cast<unsigned long long*>(state);
+  p.world = world;
+  p.rank = rank;
+  peer_rendezvous_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return cudaGetLastError();
 }
 
 int ci8_selftest_wait_timeout(unsigned deadline_us, int* gave_up, ci8_stream_t stream) {

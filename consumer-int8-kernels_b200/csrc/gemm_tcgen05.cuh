@@ -69,7 +69,32 @@ struct GemmParams {
   int out_n;                  // columns of the output matrix: n, or n / 2 for kModeSwiGLU
   int wide_tiles;             // mixed widths: the first wide_tiles channel tiles of every row stripe are
                               // tile_n + 32 columns wide, the others tile_n (0: all tiles are tile_n wide)
+  // Grouped form with a caller workspace: every tile of the last, partial wave is cut ALONG THE GROUPS
+  // into `groups` pieces that run on as many CTA pairs at once (piece_items = leftover tiles x groups
+  // work items behind the whole tiles). A piece writes its group's FP32 terms fmul(float(acc_g), sa_g)
+  // to `terms`; when all pieces of a tile have arrived (piece_sync) each of them adds the terms of its
+  // share of the tile in ascending group order (the same fadd chain as one CTA would run) and stores it.
+  int piece_items;
+  float* terms;               // [leftover tile][group][256 rows][256 columns]
+  unsigned* piece_sync;       // [leftover tile][2]: pieces' warps arrived / departed; zero before and after
 };
+
+// Grouped form: item -> the tile index tile_coords takes, the groups [g_begin, g_end) the item covers
+// and, for a piece, the index of its tile among the leftover tiles (-1 for a whole tile).
+__device__ __forceinline__ void grouped_item(const GemmParams& p, int item, int& tile, int& g_begin, int& g_end,
+                                             int& leftover) {
+  tile = item;
+  g_begin = 0;
+  g_end = p.groups;
+  leftover = -1;
+  if (p.piece_items > 0 && item >= p.full_tiles) {
+    const int q = item - p.full_tiles;
+    leftover = q / p.groups;
+    tile = p.full_tiles + leftover;
+    g_begin = q - leftover * p.groups;
+    g_end = g_begin + 1;
+  }
+}
 
 // Tensor maps of the output destinations: BF16 [M,N] matrices, boxes of 64 columns x 32 rows.
 // The gathering form can also close with a cross-GPU rendezvous inside the kernel. signal[d] points
@@ -164,6 +189,101 @@ __host__ __device__ __forceinline__ void tile_coords(const GemmParams& p, int it
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Grouped form, end of a piece: the warp reports its terms, waits until every warp of every piece of the
+// tile has done so, then adds the terms of this piece's share of the tile in ascending group order
+// and stores it.
+template <int kCtas, int kMode>
+__device__ __forceinline__ void finish_piece(float* terms, unsigned* piece_sync, const __nv_bfloat16* channel_scales,
+                                          __nv_bfloat16* out, int m, int n, int groups, int leftover, int g_begin, int mt,
+                                          int n0, int n_width, int rank, int epi, int lane, bool out_vec,
+                                          volatile int* abort_flag) {
+  using Cfg = GemmConfig<kCtas, kMode>;
+  struct { float* terms; unsigned* piece_sync; const __nv_bfloat16* sw; __nv_bfloat16* out; int m, n, groups; } p =
+      {terms, piece_sync, channel_scales, out, m, n, groups};
+  unsigned* sync = p.piece_sync + 2 * leftover;
+  const unsigned expected = static_cast<unsigned>(p.groups) * Cfg::kEpiWarps * kCtas;   // warps over all pieces
+  __threadfence();
+  __syncwarp();
+  unsigned all_in = 1u;
+  if (lane == 0) {
+    atomicAdd(sync, 1u);
+    const unsigned long long start = global_timer_ns();
+    for (uint32_t spin = 1; ld_acquire_gpu_u32(sync) < expected; ++spin) {
+      __nanosleep(64);
+      if ((spin & 255u) == 0u && (*abort_flag || global_timer_ns() - start > kWaitDeadlineNs)) {
+        atomicOr(&g_ci8_status, kStatusWaitTimeout);   // a piece never arrived: this tile stays unwritten
+        all_in = 0u;
+        break;
+      }
+    }
+  }
+  all_in = __shfl_sync(0xffffffffu, all_in, 0);
+  if (all_in) {
+    // Share of piece g_begin: vectors of 8 columns [begin, end) of the tile's 256 x 32 vectors, walked by
+    // the epilogue threads of both CTAs. Ascending-group fadd chain, then the channel scale.
+    constexpr int kTileRows = Cfg::kBlockM * kCtas, kVectors = kTileRows * (Cfg::kTileN / 8);
+    const int begin = static_cast<int>(static_cast<long long>(kVectors) * g_begin / p.groups);
+    const int end = static_cast<int>(static_cast<long long>(kVectors) * (g_begin + 1) / p.groups);
+    const int me = static_cast<int>(rank) * (Cfg::kEpiWarps * 32) + epi * 32 + lane;
+    const float* tile_terms = p.terms + static_cast<size_t>(leftover) * p.groups * kTileRows * Cfg::kTileN;
+    const int tile_row0 = mt * kTileRows;
+    for (int v = begin + me; v < end; v += kCtas * Cfg::kEpiWarps * 32) {
+      const int tile_row = v / (Cfg::kTileN / 8), col8 = (v % (Cfg::kTileN / 8)) * 8;
+      const int out_row = tile_row0 + tile_row, col = n0 + col8;
+      if (out_row >= p.m || col >= p.n || col8 >= n_width) continue;
+      const float* src = tile_terms + static_cast<size_t>(tile_row) * Cfg::kTileN + col8;
+      float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+      // four groups' terms are fetched together (one round trip to L2 for four), then added in ascending order
+#pragma unroll 1
+      for (int g0 = 0; g0 < p.groups; g0 += 4) {
+        float4 a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (g0 + i < p.groups) {
+            const float4* at = reinterpret_cast<const float4*>(src + static_cast<size_t>(g0 + i) * kTileRows * Cfg::kTileN);
+            a[i] = __ldcg(at);
+            b[i] = __ldcg(at + 1);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (g0 + i < p.groups) {
+            if (g0 + i == 0) {
+              lo = a[i];
+              hi = b[i];
+            } else {
+              lo = make_float4(__fadd_rn(lo.x, a[i].x), __fadd_rn(lo.y, a[i].y), __fadd_rn(lo.z, a[i].z), __fadd_rn(lo.w, a[i].w));
+              hi = make_float4(__fadd_rn(hi.x, b[i].x), __fadd_rn(hi.y, b[i].y), __fadd_rn(hi.z, b[i].z), __fadd_rn(hi.w, b[i].w));
+            }
+          }
+        }
+      }
+      const float sum[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+      uint32_t words[4];
+#pragma unroll
+      for (int j = 0; j < 8; j += 2) {
+        const float s0 = col + j < p.n ? __bfloat162float(p.sw[col + j]) : 0.f;
+        const float s1 = col + j + 1 < p.n ? __bfloat162float(p.sw[col + j + 1]) : 0.f;
+        words[j >> 1] = pack_bf16x2(__fmul_rn(sum[j], s0), __fmul_rn(sum[j + 1], s1));
+      }
+      __nv_bfloat16* dst = p.out + static_cast<size_t>(out_row) * p.n + col;
+      if (out_vec && col + 8 <= p.n) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(words[0], words[1], words[2], words[3]);
+      } else {
+        for (int j = 0; j < 8; ++j)
+          if (col + j < p.n)
+            reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>((j & 1) ? (words[j >> 1] >> 16) : (words[j >> 1] & 0xffffu));
+      }
+    }
+  }
+  // the last warp to leave puts the counters back to zero for the next launch
+  __syncwarp();
+  if (lane == 0 && atomicAdd(sync + 1, 1u) == expected - 1u) {
+    sync[0] = 0u;
+    sync[1] = 0u;
+  }
 }
 
 template <int kCtas, int kMode>
@@ -264,9 +384,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     const uint64_t a_policy = l2_policy_evict_last();
     bool ok = true;
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-      int mt, nt, n_start, n_width;
+      int mt, nt, n_start, n_width, g_begin = 0, g_end = p.groups, leftover = -1, tile_index = tile;
       bool alt;
-      tile_coords(p, tile, mt, nt, n_start, n_width, alt);
+      if constexpr (kMode == kModeGrouped) grouped_item(p, tile, tile_index, g_begin, g_end, leftover);
+      tile_coords(p, tile_index, mt, nt, n_start, n_width, alt);
       const int a_row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM;
       // a pair's CTAs supply half the weight rows each; slices and wide tiles load through their own box
       // (biased pair: the first CTA loads 128 channels through map_w, the second 120 through the other map)
@@ -275,7 +396,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t tx = kMode == kModeBiased
                               ? static_cast<uint32_t>(kCtas * Cfg::kABytes + Cfg::kChannelsPerTile * Cfg::kBlockK)
                               : static_cast<uint32_t>(alt ? p.stage_tx_slice : p.stage_tx) * kCtas;
-      for (int g = 0; ok && g < p.groups; ++g) {
+      for (int g = g_begin; ok && g < g_end; ++g) {
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) { ok = false; break; }
           if (elect_one()) {
@@ -306,13 +427,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       uint32_t phase = 0, acc_iter = 0;
       bool ok = true;
       for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-        int mt, nt, n_start, n_width;
+        int mt, nt, n_start, n_width, g_begin = 0, g_end = p.groups, leftover = -1, tile_index = tile;
         bool alt;
-        tile_coords(p, tile, mt, nt, n_start, n_width, alt);
+        if constexpr (kMode == kModeGrouped) grouped_item(p, tile, tile_index, g_begin, g_end, leftover);
+        tile_coords(p, tile_index, mt, nt, n_start, n_width, alt);
         // accumulator columns the MMA produces (the biased form adds its 16 ones columns)
         const uint32_t idesc = idesc_i8(Cfg::kBlockM * kCtas, kMode == kModeBiased ? Cfg::kTileN : n_width,
                                         /*b_unsigned=*/kMode == kModeBiased);
-        for (int g = 0; ok && g < p.groups; ++g, ++acc_iter) {
+        for (int g = g_begin; ok && g < g_end; ++g, ++acc_iter) {
           const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
           if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag))) { ok = false; break; }
           tcgen05_fence_after();
@@ -367,11 +489,19 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     float total[kMode == kModeGrouped ? Cfg::kColsPerEpiWarp : 1];
     for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
       int mt, nt, n0, n_width;                            // n0 = first output column of this item
+      int g_begin = 0, g_end = p.groups, leftover = -1, tile_index = tile;
       bool alt;
-      tile_coords(p, tile, mt, nt, n0, n_width, alt);
+      if constexpr (kMode == kModeGrouped) grouped_item(p, tile, tile_index, g_begin, g_end, leftover);
+      tile_coords(p, tile_index, mt, nt, n0, n_width, alt);
       const int row0 = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM + quarter * 32;
       const int row = row0 + lane;
-      for (int g = 0; g < p.groups; ++g, ++acc_iter) {
+      if constexpr (kMode == kModeGrouped) {
+        // the running sums of the previous item are dead (its first group overwrites them): say so, or
+        // they would count as live through the piece code below and push other values out of registers
+#pragma unroll
+        for (int t = 0; t < Cfg::kColsPerEpiWarp; ++t) asm volatile("" : "=f"(total[t]));
+      }
+      for (int g = g_begin; g < g_end; ++g, ++acc_iter) {
         const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
         if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(tmem_full_bar(buf), acc_phase, abort_flag))) { ok = false; break; }
         tcgen05_fence_after();
@@ -446,7 +576,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
             }
           }
         } else {
-        const bool last_group = g + 1 == p.groups;
+        const bool last_group = g + 1 == p.groups && leftover < 0;   // a piece never stores the output here
 #pragma unroll
         for (int chunk = 0; chunk < kChunks; ++chunk) {
           const int tile_col = col_base + chunk * 64;     // first accumulator column of this 64-wide box
@@ -473,7 +603,18 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
               for (int j = 0; j < 32; ++j) {
                 const float term = __fmul_rn(__int2float_rn(static_cast<int32_t>(v[j])), row_scale);
                 const int t = chunk * 64 + half * 32 + j;
-                total[t] = g == 0 ? term : __fadd_rn(total[t], term);
+                total[t] = g == g_begin ? term : __fadd_rn(total[t], term);
+              }
+              if (leftover >= 0 && tile_col + half * 32 < n_width) {
+                // a piece: this group's terms of the thread's row, 32 columns, to the workspace
+                const int tile_row = static_cast<int>(rank) * Cfg::kBlockM + quarter * 32 + lane;
+                float* dst = p.terms + ((static_cast<size_t>(leftover) * p.groups + g) * (Cfg::kBlockM * kCtas) + tile_row) * Cfg::kTileN +
+                             tile_col + half * 32;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                  const int t = chunk * 64 + half * 32 + j;
+                  __stcg(reinterpret_cast<float4*>(dst + j), make_float4(total[t], total[t + 1], total[t + 2], total[t + 3]));
+                }
               }
             }
             if (!store_box || h0 >= p.n || tile_col + half * 32 >= n_width) continue;
@@ -568,6 +709,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
         if (lane == 0) {
           if constexpr (kCtas == 2) mbar_arrive_cluster(tmem_empty_bar(buf), 0);
           else mbar_arrive(tmem_empty_bar(buf));
+        }
+      }
+      if constexpr (kMode == kModeGrouped) {
+        if (leftover >= 0) {
+          // ---- a piece: wait for the other pieces of this tile, then finish this piece's share of it
+          finish_piece<kCtas, kMode>(p.terms, p.piece_sync, p.sw, p.out, p.m, p.n, p.groups, leftover, g_begin, mt, n0, n_width,
+                                     static_cast<int>(rank), epi, lane, out_vec, abort_flag);
         }
       }
     }

@@ -221,6 +221,11 @@ __device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned 
   asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(value) : "l"(address) : "memory");
   return value;
 }
+__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* address) {
+  unsigned value;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
+  return value;
+}
 __device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* address) {
   unsigned long long value;
   asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(value) : "l"(address) : "memory");

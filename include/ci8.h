@@ -95,6 +95,22 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
                            const void* w_scale, void* out, int m, int n, int groups,
                            ci8_stream_t stream);
 
+/* ci8_grouped_channel_mm with a caller-lent workspace (no counterpart in the reference). When the tiles
+ * of the last wave would leave most of the GPU idle (M = 2048, N = 7168 on 148 SMs: 224 tiles of 256 x 256
+ * for 74 CTA pairs, so two tiles in a fourth wave), those tiles are cut along the groups: every group of
+ * such a tile runs on a CTA pair of its own, writes its FP32 terms to the workspace, and the pairs then
+ * add the terms in ascending group order, the same fadd chain as without the split, so the output
+ * has the same bits. ci8_grouped_workspace_bytes() tells how much the shape needs on the current device
+ * (0: the split would not pay and no workspace is used). The workspace must be 16-byte aligned and
+ * ZERO before its first use; the kernel leaves its counters zero again, so it can be reused by later
+ * calls in the same stream (not by calls that may overlap). A NULL or too small workspace gives the
+ * plain ci8_grouped_channel_mm. */
+long long ci8_grouped_workspace_bytes(int m, int n, int groups);
+int ci8_grouped_channel_mm_ws(const int8_t* codes, const int8_t* w, const float* scales,
+                              const void* w_scale, void* out, void* workspace,
+                              long long workspace_bytes, int m, int n, int groups,
+                              ci8_stream_t stream);
+
 /* quantize_rows followed by fused_channel_mm as one call (reference csrc/kernels.cu:283-292 then
  * csrc/fused_mm.cu:66-93; the reference always launches the two separately). x BF16 [m,k], w INT8
  * [n,k], w_scale BF16 [n] -> out BF16 [m,n]; codes INT8 [m,k] and scales FP32 [m] receive exactly what
@@ -186,6 +202,14 @@ int ci8_fused_channel_mm_gather_sync(const int8_t* a, const int8_t* w, const flo
                                      const void* w_scale, void* const* gathered, void* const* signals,
                                      void* state, int world, int rank, int m, int n_shard, int k,
                                      int schedule, ci8_stream_t stream);
+
+/* The closing barrier of ci8_fused_channel_mm_gather as a one-thread kernel of its own (no counterpart
+ * in the reference): ordered after the gathering GEMM in the stream, it tells every peer that this
+ * rank's stores are complete and waits until every peer has said the same, so that what follows in
+ * the stream sees the whole gathered result. signals and state as for
+ * ci8_fused_channel_mm_gather_sync (each caller needs its own state and counters: do not share them
+ * with that entry point). Bounded like every wait: 2 s, then status bit 2. */
+int ci8_peer_rendezvous(void* const* signals, void* state, int world, int rank, ci8_stream_t stream);
 
 /* The streaming (m <= 64) kernel behind ci8_fused_channel_mm / ci8_cutlass_channel_mm /
  * ci8_channel_mm with the split-K factor forced to 1, 2 or 4 (1 or 2 for m > 16) instead of chosen

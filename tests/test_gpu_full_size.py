@@ -103,6 +103,14 @@ def test_grouped_config(ops):
     want = ref.grouped_channel_mm_ref(want_codes[:, rows].contiguous(), want_scales[:, rows].contiguous(),
                                       inputs.w, inputs.w_scale, fast=True)
     assert_bit_equal(out[rows.to(DEV)], want, "sampled rows")
+    # the same with a lent workspace: the two tiles of the fourth wave run split along the groups
+    need = ops.grouped_workspace_bytes(m, n, groups)
+    if need:
+        workspace = torch.zeros(need, dtype=torch.uint8, device=DEV)
+        split = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+        for _ in range(2):
+            ops.grouped_channel_mm_ws(codes, inputs.w.to(DEV), scales, inputs.w_scale.to(DEV), workspace, split)
+        assert torch.equal(out, split), "the split along the groups changed the result"
     assert device_status(ops) == 0
 
 

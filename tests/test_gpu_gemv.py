@@ -58,3 +58,32 @@ def test_w8a16_with_activations_that_are_only_4_byte_aligned(ops, m, n, k):
     aligned = torch.empty_like(out)
     ops.channel_gemv(x.clone(), weight, scale, aligned)
     torch.testing.assert_close(aligned.cpu(), reference, atol=0.004, rtol=0.008)
+
+
+@pytest.mark.parametrize("n", [64, 2304])     # the register-fed kernel (small N) and the TMA-staged one
+def test_dequantised_weights_are_the_reference_rounding_bit_for_bit(ops, n):
+    """The operator multiplies activations with bf16(float(code) * float(scale)) (the reference's
+    csrc/gemv.cu:23-26). With one-hot activation rows the output IS that multiplicand, so every code from
+    -128 to 127 against a spread of scales (tiny, ordinary, large, negative) can be compared exactly with
+    ``(w.float() * scale.float()).bfloat16()``."""
+    k = 256
+    codes = torch.arange(-128, 128, dtype=torch.int16).to(torch.int8)
+    weight = codes.repeat(n, 1).contiguous()                        # channel c, position j holds code j - 128
+    generator = torch.Generator().manual_seed(5)
+    scale = (torch.rand(n, generator=generator) * 0.02 + 1e-4)
+    scale[::7] *= 1e-30
+    scale[1::7] *= 1e20
+    scale[2::7] *= -1.0
+    scale = scale.bfloat16()
+    want = (weight.float() * scale.float()[:, None]).bfloat16()     # [n, k]
+    dw, ds = weight.to(DEV), scale.to(DEV)
+    out = torch.empty(16, n, dtype=torch.bfloat16, device=DEV)
+    for first in range(0, k, 16):
+        x = torch.zeros(16, k, dtype=torch.bfloat16)
+        x[torch.arange(16), first + torch.arange(16)] = 1.0          # row i picks position first + i
+        ops.channel_gemv(x.to(DEV), dw, ds, out)
+        got = out.cpu()                                              # got[i, c] = multiplicand of (c, first + i)
+        expected = want[:, first:first + 16].T.contiguous()
+        # (code 0 times a negative scale is -0, which the sum with the other, +0, products turns into +0)
+        expected = torch.where(expected == 0, torch.zeros_like(expected), expected)
+        assert torch.equal(got.view(torch.int16), expected.view(torch.int16)), f"positions {first}..{first + 15}"

@@ -47,6 +47,64 @@ def test_grouped_mixed_tile_widths_match_checker(ops):
     assert device_status(ops) == 0
 
 
+@pytest.mark.parametrize("m,n,groups", [(300, 512, 3), (520, 700, 4), (300, 250, 5), (257, 256, 16), (2048, 7168, 2)])
+def test_grouped_split_along_the_groups_matches_checker(ops, m, n, groups):
+    """With a lent workspace the tiles of a thin last wave run as one piece per group on CTA pairs of their
+    own and the pieces add their FP32 terms in ascending group order: same bits as the checker and as
+    the plain operator, call after call on the same workspace (its counters return to zero)."""
+    need = ops.grouped_workspace_bytes(m, n, groups)
+    assert need > 0, "this shape no longer exercises the split along the groups"
+    inputs = workloads.grouped_inputs(m, n, groups, seed=m + n)
+    codes, scales = ref.quantize_grouped4096_ref(inputs.x)
+    want = ref.grouped_channel_mm_ref(codes, scales, inputs.w, inputs.w_scale, fast=True)
+    dc, dw, ds, dsw = codes.to(DEV), inputs.w.to(DEV), scales.to(DEV), inputs.w_scale.to(DEV)
+    workspace = torch.zeros(need, dtype=torch.uint8, device=DEV)
+    for call in range(3):
+        out, check = guarded((m, n), torch.bfloat16, float("nan"))
+        ops.grouped_channel_mm_ws(dc, dw, ds, dsw, workspace, out)
+        assert_bit_equal(out, want, f"split along the groups, call {call}")
+        check()
+    assert int(workspace[:1024].view(torch.int32).abs().sum()) == 0, "the counters did not return to zero"
+    plain = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    ops.grouped_channel_mm(dc, dw, ds, dsw, plain)
+    assert_bit_equal(plain, want, "plain operator")
+    # a workspace that is too small is ignored, not an error
+    ops.grouped_channel_mm_ws(dc, dw, ds, dsw, workspace[:16], plain)
+    assert_bit_equal(plain, want, "too small a workspace")
+    assert device_status(ops) == 0
+
+
+def test_grouped_split_replays_from_a_graph(ops):
+    m, n, groups = 520, 700, 4
+    need = ops.grouped_workspace_bytes(m, n, groups)
+    assert need > 0
+    inputs = workloads.grouped_inputs(m, n, groups, seed=8)
+    x = inputs.x.to(DEV)
+    dw, dsw = inputs.w.to(DEV), inputs.w_scale.to(DEV)
+    codes = torch.empty(groups, m, 4096, dtype=torch.int8, device=DEV)
+    scales = torch.empty(groups, m, device=DEV)
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+    workspace = torch.zeros(need, dtype=torch.uint8, device=DEV)
+
+    def run():
+        ops.quantize_grouped4096(x, codes, scales)
+        ops.grouped_channel_mm_ws(codes, dw, scales, dsw, workspace, out)
+
+    run()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run()
+    for replay in range(2):
+        x.neg_()
+        out.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        rc, rs = ref.quantize_grouped4096_ref(x.cpu())
+        assert_bit_equal(out, ref.grouped_channel_mm_ref(rc, rs, inputs.w, inputs.w_scale, fast=True), f"replay {replay}")
+    assert device_status(ops) == 0
+
+
 def test_one_group_equals_fused_channel_mm(ops):
     inputs = workloads.grouped_inputs(200, 512, 1, seed=2)
     codes, scales = ref.quantize_grouped4096_ref(inputs.x)
