@@ -316,6 +316,20 @@ cudaError_t launch_gemm(const void* a, const void* w, const GemmParams& base, cu
     return cudaErrorInvalidValue;   // several destinations, and the SwiGLU form, need the tile-store path
   }
 
+  if (kMode == kModeWorkspace && p.workspace && p.n % 4 == 0 && aligned(p.workspace, 16)) {
+    EncodeTiled encode = encode_tiled_fn();
+    if (!encode) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.n), static_cast<cuuint64_t>(p.m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.n) * 4};
+    const cuuint32_t box[2] = {32u, 32u};
+    const cuuint32_t elem[2] = {1u, 1u};
+    const CUresult r = encode(&out_maps.ws_map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, p.workspace, dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    out_maps.has_ws_map = 1;
+  }
+
   const long long tiles = p.total_items;
   cudaLaunchConfig_t config = {};
   cudaLaunchAttribute attr[2];
@@ -622,6 +636,17 @@ channel_mm_words_kernel(const int8_t* __restrict__ a, const uint8_t* __restrict_
   }
 }
 
+// Moves the device status word into a caller-owned word on the stream (and clears it), so that a
+// captured graph can carry the check: bits are ORed into *word, which may be device memory or pinned,
+// device-mapped host memory that the host polls and clears at its leisure.
+__global__ void status_to_word_kernel(unsigned* word) {
+  const unsigned bits = atomicExch(&g_ci8_status, 0u);
+  if (bits) {
+    atomicOr_system(word, bits);
+    __threadfence_system();
+  }
+}
+
 // Self-test of the bounded wait: one CTA waits on an mbarrier that nothing ever arrives on. The
 // wait gives up after `deadline_ns`, raises the status bit and the kernel returns normally.
 __global__ void wait_timeout_selftest_kernel(unsigned long long deadline_ns, int* gave_up) {
@@ -764,6 +789,12 @@ int ci8_device_status(unsigned* status) {
   if (err != cudaSuccess) return err;
   const unsigned zero = 0;
   return cudaMemcpyToSymbol(ci8::g_ci8_status, &zero, sizeof(unsigned));
+}
+
+int ci8_device_status_async(unsigned* word, ci8_stream_t stream) {
+  if (!word || !aligned(word, 4)) return kInvalid;
+  status_to_word_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(word);
+  return cudaGetLastError();
 }
 
 int ci8_quantize_rows(const void* x, int8_t* codes, float* scales, int m, int k, ci8_stream_t stream) {

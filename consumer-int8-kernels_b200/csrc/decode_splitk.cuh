@@ -302,7 +302,7 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
           for (int j = 0; j < 4; ++j)
             packed_max = absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(absmax_bf16x2(packed_max, v[rr][j].x), v[rr][j].y),
                                                      v[rr][j].z), v[rr][j].w);
-          float maximum = fmaxf(bf16_lo(packed_max), bf16_hi(packed_max));
+          float maximum = fmaxf(absmax_lo(packed_max), absmax_hi(packed_max));
 #pragma unroll
           for (int mask = 16; mask; mask >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, mask));
           if (lane == 0) partial[(r0 + rr) * 8 + warp] = maximum;

@@ -110,6 +110,10 @@ struct OutputMaps {
   unsigned long long* signal[kMaxOutputs];
   unsigned long long* state;      // nullptr: no rendezvous, the caller orders a barrier after the call
   int source;                     // this rank
+  // workspace form: the INT32 accumulator matrix [M,N] as boxes of 32 columns x 32 rows (has_ws_map != 0
+  // when its pitch and base allow tile stores; otherwise the accumulators leave through direct stores)
+  CUtensorMap ws_map;
+  int has_ws_map;
 };
 
 template <int kCtas, int kMode>
@@ -125,13 +129,15 @@ struct GemmConfig {
   static constexpr int kABytes = kBlockM * kBlockK;
   static constexpr int kBBytes = kBRowsSmem * kBlockK;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = kCtas == 1 ? 4 : 6;
+  // (the workspace form gives one ring stage to the staging boxes of its INT32 tile stores)
+  static constexpr int kStages = (kCtas == 1 ? 4 : 6) - (kMode == kModeWorkspace ? 1 : 0);
   static constexpr int kEpiWarps = kMode == kModeGrouped ? 8 : 4;
   static constexpr int kThreads = (2 + kEpiWarps) * 32;
   static constexpr int kColsPerEpiWarp = kTileN / (kEpiWarps / 4);
   static constexpr int kStoreBoxBytes = 32 * 128;     // one staged store box: 32 rows x 64 BF16
   static constexpr int kStoreBufs = kEpiWarps == 4 ? 2 : 1;   // staging boxes per epilogue warp
-  static constexpr int kStagingBytes = kEpiWarps * kStoreBufs * kStoreBoxBytes;
+  static constexpr int kWsBufs = kMode == kModeWorkspace ? 2 : 0;   // INT32 staging boxes (32 x 32) per epilogue warp
+  static constexpr int kStagingBytes = kEpiWarps * (kStoreBufs + kWsBufs) * kStoreBoxBytes;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
   static_assert(kSmemBytes <= 232448, "shared memory budget");
@@ -482,7 +488,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     const bool tma_out = p.num_outputs > 0;
     const bool out_vec = (p.n % 8 == 0) && (reinterpret_cast<uintptr_t>(p.out) % 16 == 0);
     const bool ws_vec = (p.n % 4 == 0) && (reinterpret_cast<uintptr_t>(p.workspace) % 16 == 0);
-    uint8_t* my_staging = staging + epi * Cfg::kStoreBufs * Cfg::kStoreBoxBytes;
+    uint8_t* my_staging = staging + epi * (Cfg::kStoreBufs + Cfg::kWsBufs) * Cfg::kStoreBoxBytes;
+    uint8_t* my_ws_staging = my_staging + Cfg::kStoreBufs * Cfg::kStoreBoxBytes;
+    const bool ws_tma = kMode == kModeWorkspace && out_maps.has_ws_map != 0;
     uint32_t acc_iter = 0, store_iter = 0;
     bool ok = true;
     const uint64_t store_policy = l2_policy_evict_first();
@@ -628,7 +636,24 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
               for (int j = 0; j < 32; ++j) v[j] = static_cast<uint32_t>(static_cast<int32_t>(v[j]) - bias);
             }
             if constexpr (kMode == kModeWorkspace) {
-              if (row < p.m) {
+              if (ws_tma) {
+                // The accumulators leave as a 32 x 32 INT32 tile store (128-byte rows, same swizzle as the BF16
+                // boxes). Two staging boxes alternate; letting at most one store group stay pending before a box
+                // is written again is enough: whatever was committed before the latest group has then been read.
+                uint8_t* ws_box = my_ws_staging + half * Cfg::kStoreBoxBytes;
+                if (lane == 0) tma_store_wait_read<1>();
+                __syncwarp();
+                uint4* ws_row = reinterpret_cast<uint4*>(ws_box + lane * 128);
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                  ws_row[c ^ (lane & 7)] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && row0 < p.m) {
+                  tma_store_2d(&out_maps.ws_map, smem_u32(ws_box), h0, row0);
+                  tma_store_commit();
+                }
+              } else if (row < p.m) {
                 int32_t* ws = p.workspace + static_cast<size_t>(row) * p.n + h0;
                 if (ws_vec && limit >= 32) {
 #pragma unroll
@@ -719,7 +744,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
     }
-    if (tma_out && lane == 0) {
+    if ((tma_out || ws_tma) && lane == 0) {
       // staged boxes must outlive their stores; before the rendezvous the stores must have landed as well
       if (out_maps.state) tma_store_wait_all(); else tma_store_wait_read<0>();
     }

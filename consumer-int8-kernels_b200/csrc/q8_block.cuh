@@ -47,7 +47,7 @@ q8_block_quantize_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
     packed_max = absmax_bf16x2(packed_max, pack[i].z);
     packed_max = absmax_bf16x2(packed_max, pack[i].w);
   }
-  const float maximum = fmaxf(bf16_lo(packed_max), bf16_hi(packed_max));
+  const float maximum = fmaxf(absmax_lo(packed_max), absmax_hi(packed_max));
   const float scale = fmaxf(__fdiv_rn(maximum, 127.f), 1e-20f);
   const float inverse = __fdiv_rn(1.f, scale);
   uint2 codes[4];

@@ -38,12 +38,19 @@ constexpr float kTieGuard = 0.49995f;       // |q' - rint(q')| below this: no ti
 // from that integer. |v * inverse - v / scale| <= 127.5 * 2^-24 and the reference's own rounding of
 // v / scale moves it by as much again, so outside the guard band both round alike. NaN compares
 // false, so NaN and inf * 0 land on the exact path too.
-__device__ __forceinline__ float2 quantize_fast2(float2 v, float2 inverse, bool& safe) {
+// `worst` collects the largest |residual| of a pack with one instruction per value (magnitude of the
+// larger operand, NaN kept), so the pack needs a single comparison at its end.
+__device__ __forceinline__ float max_abs_keep_nan(float a, float b) {
+  float r;
+  asm("max.NaN.xorsign.abs.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float2 quantize_fast2(float2 v, float2 inverse, float& worst) {
   const float2 magic = make_float2(kRoundMagic, kRoundMagic);
   const float2 shifted = __ffma2_rn(v, inverse, magic);
   const float2 minus_rounded = __ffma2_rn(shifted, make_float2(-1.f, -1.f), magic);   // exact
   const float2 residual = __ffma2_rn(v, inverse, minus_rounded);
-  safe = safe && (fabsf(residual.x) < kTieGuard) && (fabsf(residual.y) < kTieGuard);
+  worst = max_abs_keep_nan(max_abs_keep_nan(worst, residual.x), residual.y);
   return shifted;
 }
 // The same test for one value (used by the repair path to find the offender).
@@ -53,13 +60,17 @@ __device__ __forceinline__ bool away_from_tie(float v, float inverse) {
   return fabsf(residual) < kTieGuard;
 }
 
-// Running maximum of |x| over packed BF16 pairs: one LOP3 and one packed max per two values. The
-// packed max returns the other operand when one is NaN, which is what fmaxf does.
+// Running maximum of |x| over packed BF16 pairs: one packed instruction per two values (the larger
+// magnitude of each half; the sign bits it returns are meaningless and are masked where the maximum is
+// read). It returns the other operand when one is NaN, which is what fmaxf does.
 __device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t running, uint32_t pair) {
   uint32_t result;
-  asm("max.bf16x2 %0, %1, %2;" : "=r"(result) : "r"(running), "r"(pair & 0x7fff7fffu));
+  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(result) : "r"(running), "r"(pair));
   return result;
 }
+// The two maxima of a running packed maximum, as non-negative floats.
+__device__ __forceinline__ float absmax_lo(uint32_t running) { return __uint_as_float((running << 16) & 0x7fffffffu); }
+__device__ __forceinline__ float absmax_hi(uint32_t running) { return __uint_as_float(running & 0x7fff0000u); }
 
 // Eight BF16 values (one 16-byte pack) -> eight codes (8 bytes). BF16 inputs hit exact rounding ties
 // far more often than random reals would (x * 127 / absmax is a ratio of small integers): about one
@@ -70,14 +81,14 @@ __device__ __forceinline__ uint2 quantize_pack(const uint4& pack, float scale, f
                       bf16_lo(pack.z), bf16_hi(pack.z), bf16_lo(pack.w), bf16_hi(pack.w)};
   const float2 inverse2 = make_float2(inverse, inverse);
   uint32_t t[8];
-  bool safe = true;
+  float worst = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; j += 2) {
-    const float2 shifted = quantize_fast2(make_float2(v[j], v[j + 1]), inverse2, safe);
+    const float2 shifted = quantize_fast2(make_float2(v[j], v[j + 1]), inverse2, worst);
     t[j] = __float_as_uint(shifted.x);
     t[j + 1] = __float_as_uint(shifted.y);
   }
-  if (!safe) {
+  if (!(fabsf(worst) < kTieGuard)) {   // also taken when a residual is NaN (NaN or infinite inputs)
 #pragma unroll
     for (int j = 0; j < 8; ++j)
       if (!away_from_tie(v[j], inverse)) t[j] = static_cast<uint32_t>(quantize_one(v[j], scale));
@@ -170,7 +181,7 @@ quantize_rows_vec_kernel(const uint16_t* __restrict__ x, int8_t* __restrict__ q,
       packed_max = absmax_bf16x2(packed_max, pack[i].z);
       packed_max = absmax_bf16x2(packed_max, pack[i].w);
     }
-    float maximum = fmaxf(bf16_lo(packed_max), bf16_hi(packed_max));
+    float maximum = fmaxf(absmax_lo(packed_max), absmax_hi(packed_max));
 #pragma unroll
     for (int mask = 16; mask; mask >>= 1)
       maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, mask));

@@ -245,6 +245,14 @@ int ci8_selftest_cluster_timeout(unsigned deadline_us, int* gave_up, ci8_stream_
  * ci8_fused_channel_mm_gather_sync did (a peer never arrived). Returns 0 or a cudaError_t. Not for use during stream capture. */
 int ci8_device_status(unsigned* status);
 
+/* The same check without a synchronisation, for serving loops that replay CUDA graphs (no counterpart in
+ * the reference): enqueues a one-thread kernel that ORs the status word into *word and clears it. word
+ * is caller-owned, 4-byte aligned, device memory or pinned host memory mapped into the device; it is
+ * only ever ORed into, so the host may read it at any time and clear it when it has acted on it. Put
+ * one such call at the end of a captured step and poll the word every few steps: a non-zero value means
+ * that a kernel of an earlier step gave up on a wait and that step's output is not to be trusted. */
+int ci8_device_status_async(unsigned* word, ci8_stream_t stream);
+
 /* Text for a code returned by any function above. */
 const char* ci8_error_string(int code);
 

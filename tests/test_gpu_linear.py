@@ -347,3 +347,28 @@ def test_a_cluster_rendezvous_that_runs_out_sets_its_own_status_bit(ops):
         assert rc == 0
         assert_bit_equal(out, want, f"split-K {split} after a timed-out rendezvous")
     assert device_status(ops) == 0
+
+
+def test_status_word_can_be_collected_inside_a_captured_graph(ops):
+    """ci8_device_status synchronises and cannot be captured; ci8_device_status_async moves the word into a
+    caller-owned word on the stream instead. Captured behind a wait that runs out, a replay leaves the
+    bit in that word and the library's own word clear."""
+    assert device_status(ops) == 0
+    gave_up = torch.zeros(1, dtype=torch.int32, device=DEV)
+    word = torch.zeros(1, dtype=torch.int32, device=DEV)
+    lib = ops.libci8
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        stream = ctypes.c_void_p(side.cuda_stream)
+        assert lib.ci8_device_status_async(ctypes.c_void_p(word.data_ptr()), stream) == 0     # warm-up, nothing to report
+        torch.cuda.synchronize()
+        assert word.item() == 0
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            assert lib.ci8_selftest_wait_timeout(5000, ctypes.c_void_p(gave_up.data_ptr()), stream) == 0
+            assert lib.ci8_device_status_async(ctypes.c_void_p(word.data_ptr()), stream) == 0
+        graph.replay()
+        torch.cuda.synchronize()
+    assert gave_up.item() == 1 and word.item() == 1
+    assert device_status(ops) == 0           # the library's word was cleared by the collecting kernel
+    assert lib.ci8_device_status_async(ctypes.c_void_p(0), ctypes.c_void_p(0)) == 1

@@ -34,16 +34,19 @@ def _small_shapes(rank, world, device, outcome):
         codes, scales = ref.quantize_rows_ref(inputs.x)
         _, want = ref.fused_channel_mm_ref(codes, inputs.w, scales, inputs.w_scale, fast=True)
         x = inputs.x.to(device)
-        for mode, chunks in (("fused", 1), ("fused_flag", 1), ("fused_nccl_barrier", 1), ("nccl", 1), ("nccl", 3 if m % 3 == 0 else 1)):
-            plan = ShardPlan(m, n, k, world, rank, chunks)
+        for mode, chunks in (("fused", 1), ("fused_flag", 1), ("fused_nccl_barrier", 1), ("copy_engine", 3), ("nccl", 1),
+                             ("nccl", 3 if m % 3 == 0 else 1)):
+            plan = ShardPlan(m, n, k, world, rank, chunks if mode != "copy_engine" else 1)
             w_shard, sw_shard = plan.shard_weights(inputs.w, inputs.w_scale)
-            layer = ColumnShardedLinear(plan, w_shard.to(device), sw_shard.to(device), mode=mode)
+            layer = ColumnShardedLinear(ShardPlan(m, n, k, world, rank, chunks) if mode == "copy_engine" else plan,
+                                        w_shard.to(device), sw_shard.to(device), mode=mode)
             for s in layer._sets:
                 s["gathered"].fill_(float("nan"))
             layer.gathered.fill_(float("nan"))
             torch.cuda.synchronize()
             dist.barrier()
             for call in range(3):       # three calls: both buffer sets, then the first one again (overwritten)
+                dist.barrier()          # the in-kernel rendezvous gives up after 2 s: enter together
                 gathered = layer.forward(x)
                 torch.cuda.synchronize()
                 outcome[f"{mode}/{chunks}/{m}x{n}x{k}/call{call}"] = _same(plan.row_major(gathered).cpu(), want)
@@ -73,6 +76,7 @@ def _graph_replay(rank, world, device, outcome):
     x = inputs.x.to(device)
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
+        dist.barrier()
         layer.forward(x)
         layer.forward(x)
         torch.cuda.synchronize()
@@ -117,6 +121,7 @@ def _full_size_shard(rank, world, device, outcome):
     codes, scales = ref.quantize_rows_ref(x_host[rows])
     _, want = ref.fused_channel_mm_ref(codes, w, scales, w_scale, fast=True)
     for call in range(2):
+        dist.barrier()                  # the checker above takes a different time on every rank
         gathered = layer.forward(x)
         torch.cuda.synchronize()
         got = gathered[0][:, rows.to(device)].permute(1, 0, 2).reshape(len(rows), n).cpu()
