@@ -244,11 +244,10 @@ def run_ours(args, spec, rank, world, local_rank):
     x_host = workloads.activations(m, k, gen).pin_memory()
     w, w_scale = workloads.weights(n, k, gen)
     mode = args.gather if world > 1 else "nccl"
-    fused = mode in ("fused", "fused_flag", "fused_nccl_barrier", "copy_engine")     # symmetric memory, two buffer sets
-    plan = ShardPlan(m, n, k, world, rank, chunks=args.chunks if mode in ("nccl", "copy_engine") and world > 1 else 1)
+    fused = mode in ("fused", "fused_flag", "fused_nccl_barrier")     # symmetric memory, two buffer sets
+    plan = ShardPlan(m, n, k, world, rank, chunks=args.chunks if mode == "nccl" and world > 1 else 1)
     w_shard, sw_shard = plan.shard_weights(w, w_scale)
     layer = ColumnShardedLinear(plan, w_shard.to(device), sw_shard.to(device), schedule=args.schedule, mode=mode)
-    plan = layer.plan       # (the copy-engine mode keeps its row chunks inside the one-chunk layout)
     x = x_host.to(device)
     out_host = torch.empty(m, plan.shard_n, dtype=torch.bfloat16).pin_memory()
 
@@ -257,6 +256,7 @@ def run_ours(args, spec, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
+    barrier()       # the ranks enter the first call together (the in-kernel rendezvous gives up after 2 s)
     for _ in range(max(args.warmup, 3)):
         gathered = layer.forward(x)
     barrier()
@@ -395,16 +395,15 @@ def run_ours(args, spec, rank, world, local_rank):
                             "an in-kernel rendezvous" if mode == "fused" else
                             "fused stores closed by a one-thread rendezvous kernel" if mode == "fused_flag" else
                             "fused stores closed by an NCCL barrier" if mode == "fused_nccl_barrier" else
-                            f"copy engines push {args.chunks} row chunks to every peer behind the GEMM; rendezvous kernel" if mode == "copy_engine" else
                             "NCCL all-gather of BF16 [M,N/G] blocks"),
-                    row_chunks=max(plan.chunks, layer.row_chunks), schedule=args.schedule,
+                    row_chunks=plan.chunks, schedule=args.schedule,
                     parity="32 seeded rows of the whole result on every rank, bit for bit against the CPU checker, before timing",
                     l2="inputs larger than L2 (weights+activations+output per step exceed 126 MB); no flush"),
         roofline=roofline,
         e2e=dict(value=ops_total / (e2e_ms * 1e-3) / 1e12, unit="TOPS", h2d_bytes_per_step=x_host.numel() * 2,
                  d2h_bytes_per_step=out_host.numel() * 2, ms_per_step=e2e_ms, steps=e2e_steps,
                  note="per rank: the activations in, this rank's [M, N/G] block out (the whole result reaches the host once)"),
-        gpu_launches=args.steps * (1 + max(plan.chunks, layer.row_chunks) + (1 if mode in ('fused_flag', 'copy_engine') else 0)), clocks=clocks.summary(), device_status=word.value,
+        gpu_launches=args.steps * (1 + plan.chunks + (1 if mode == 'fused_flag' else 0)), clocks=clocks.summary(), device_status=word.value,
     )
     if world > 1:
         bytes_in = plan.gather_bytes_received
@@ -707,11 +706,11 @@ def main():
     parser.add_argument("--profile-only", action="store_true",
                         help="run --steps launches of the workload's kernels with no timing (for ncu captures)")
     parser.add_argument("--schedule", type=int, default=0)
-    parser.add_argument("--gather", choices=["fused", "fused_flag", "fused_nccl_barrier", "copy_engine", "nccl"], default="fused",
+    parser.add_argument("--gather", choices=["fused", "fused_flag", "fused_nccl_barrier", "nccl"], default="fused",
                         help="N>1: peer stores from the GEMM epilogue (closed inside the kernel, or by an NCCL "
                              "barrier), or a separate NCCL all-gather")
     parser.add_argument("--chunks", type=int, default=4,
-                        help="--gather nccl / copy_engine: row chunks whose transfer overlaps the next chunk's GEMM")
+                        help="--gather nccl: row chunks whose gather overlaps the next GEMM")
     parser.add_argument("--no-extra", action="store_true", help="skip the other benchmark configs")
     args = parser.parse_args()
     spec = WORKLOADS[args.workload]

@@ -19,11 +19,6 @@ Ways to move it (``mode``):
   one-thread kernel behind it (``ops.peer_rendezvous``) exchanges the arrival counts.
 * ``"fused_nccl_barrier"``: the same stores, closed by a small stream-ordered NCCL all-reduce instead
   (the first form of this path; kept for comparison).
-* ``"copy_engine"``: the GEMM runs in ``chunks`` row chunks that write only this rank's block; behind each
-  chunk the GPU's copy engines (plain peer-to-peer ``cudaMemcpyAsync`` on one side stream per peer) push
-  that chunk into every peer's buffer while the next chunk computes, and ``ops.peer_rendezvous`` closes
-  the call. No SM takes part in the transfer, so it does not slow the GEMM down; the price is one more
-  read of the block from this GPU's memory and a tail of one chunk's copy.
 * ``"nccl"``: the GEMM writes its block locally and one NCCL all-gather moves it.
 * ``"none"``: no gather at all: the result stays column-sharded, ``[M, N/G]`` per rank in block ``rank``
   of the returned buffer. A row-parallel layer that follows (the down projection after a column-
@@ -100,9 +95,8 @@ class ShardPlan:
         return gathered.permute(0, 2, 1, 3).reshape(self.m, self.n)
 
 
-MODES = ("fused", "fused_flag", "fused_nccl_barrier", "copy_engine", "nccl", "none")
+MODES = ("fused", "fused_flag", "fused_nccl_barrier", "nccl", "none")
 FUSED_MODES = ("fused", "fused_flag", "fused_nccl_barrier")
-SYMMETRIC_MODES = FUSED_MODES + ("copy_engine",)
 
 
 class ColumnShardedLinear:
@@ -136,13 +130,7 @@ class ColumnShardedLinear:
         self.mode = mode if plan.world > 1 else "nccl"
         self.calls = 0
         self._sets = []            # fused modes: two sets of (gathered, peer_ptrs, signal_ptrs, state, handles)
-        self.row_chunks = 1
-        if self.mode == "copy_engine":
-            # the row chunks live inside the one-chunk layout [1, G, M, N/G]: rows of a block are contiguous
-            self.row_chunks = plan.chunks
-            plan = ShardPlan(plan.m, plan.n, plan.k, plan.world, plan.rank, 1)
-            self.plan = plan
-        if self.mode in SYMMETRIC_MODES:
+        if self.mode in FUSED_MODES:
             if plan.chunks != 1:
                 raise ValueError("the fused gather overlaps tile by tile; use chunks=1")
             if plan.shard_n % 8:
@@ -157,9 +145,6 @@ class ColumnShardedLinear:
                 counters.zero_()
                 counter_handle = symm_mem.rendezvous(counters, group=where)
                 self._sets.append(dict(
-                    # every rank's buffer as a tensor of this process ([G, M, N/G]); only the copy-engine mode uses them
-                    peers=[handle.get_buffer(r, (plan.world, plan.m, plan.shard_n), torch.bfloat16) for r in range(plan.world)]
-                    if self.mode == "copy_engine" else None,
                     gathered=flat.view(plan.gathered_shape),
                     peer_ptrs=torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64),
                     signal_ptrs=torch.tensor([int(p) for p in counter_handle.buffer_ptrs], dtype=torch.int64),
@@ -172,10 +157,6 @@ class ColumnShardedLinear:
             self._barrier_word = torch.zeros(1, dtype=torch.float32, device=device)
         else:
             self.gathered = torch.empty(plan.gathered_shape, dtype=torch.bfloat16, device=device)
-        if self.mode == "copy_engine":
-            self._peer_streams = [torch.cuda.Stream(device=device) for _ in range(plan.world - 1)]
-            self._rows_done = [torch.cuda.Event() for _ in range(self.row_chunks)]
-            self._copies_done = [torch.cuda.Event() for _ in range(plan.world - 1)]
         overlap = self.mode == "nccl" and plan.chunks > 1 and plan.world > 1 and device.type == "cuda"
         self.comm_stream = torch.cuda.Stream(device=device) if overlap else None
         self._chunk_done = [torch.cuda.Event() for _ in range(plan.chunks)] if self.comm_stream else []
@@ -198,8 +179,6 @@ class ColumnShardedLinear:
             self.compute(x)
             return self.gathered
         self.ops.quantize_rows(x, self.codes, self.scales)
-        if self.mode == "copy_engine":
-            return self._forward_copy_engine()
         if self.mode in FUSED_MODES:
             # every rank writes its block into every rank's buffer; the two sets alternate so that a
             # rank already in its next call cannot overwrite a result a peer still reads
@@ -234,31 +213,4 @@ class ColumnShardedLinear:
                     dist.all_gather_into_tensor(flat, mine, group=self.group)
         if self.comm_stream is not None:
             main.wait_stream(self.comm_stream)
-        return self.gathered
-
-    def _forward_copy_engine(self) -> torch.Tensor:
-        """Row chunks of this rank's GEMM, each pushed to every peer by the copy engines while the next one
-        computes; the rendezvous kernel on the main stream closes the call."""
-        plan = self.plan
-        current = self._sets[self.calls % 2]
-        self.calls += 1
-        self.gathered = current["gathered"]
-        mine = self.gathered[0, plan.rank]                 # [M, N/G]
-        main = torch.cuda.current_stream()
-        step = -(-plan.m // self.row_chunks)
-        for c in range(self.row_chunks):
-            rows = slice(c * step, min(plan.m, (c + 1) * step))
-            if rows.start >= plan.m:
-                break
-            self.ops.fused_channel_mm(self.codes[rows], self.w, self.scales[rows], self.w_scale, mine[rows], self.schedule)
-            self._rows_done[c].record(main)
-            for d, stream in enumerate(self._peer_streams, start=1):
-                peer = (plan.rank + d) % plan.world        # every rank walks its peers in a different order
-                stream.wait_event(self._rows_done[c])
-                with torch.cuda.stream(stream):
-                    current["peers"][peer][plan.rank, rows].copy_(mine[rows], non_blocking=True)
-        for d, stream in enumerate(self._peer_streams):
-            self._copies_done[d].record(stream)
-            main.wait_event(self._copies_done[d])
-        self.ops.peer_rendezvous(current["signal_ptrs"], current["state"], plan.rank)
         return self.gathered

@@ -34,12 +34,10 @@ def _small_shapes(rank, world, device, outcome):
         codes, scales = ref.quantize_rows_ref(inputs.x)
         _, want = ref.fused_channel_mm_ref(codes, inputs.w, scales, inputs.w_scale, fast=True)
         x = inputs.x.to(device)
-        for mode, chunks in (("fused", 1), ("fused_flag", 1), ("fused_nccl_barrier", 1), ("copy_engine", 3), ("nccl", 1),
-                             ("nccl", 3 if m % 3 == 0 else 1)):
-            plan = ShardPlan(m, n, k, world, rank, chunks if mode != "copy_engine" else 1)
+        for mode, chunks in (("fused", 1), ("fused_flag", 1), ("fused_nccl_barrier", 1), ("nccl", 1), ("nccl", 3 if m % 3 == 0 else 1)):
+            plan = ShardPlan(m, n, k, world, rank, chunks)
             w_shard, sw_shard = plan.shard_weights(inputs.w, inputs.w_scale)
-            layer = ColumnShardedLinear(ShardPlan(m, n, k, world, rank, chunks) if mode == "copy_engine" else plan,
-                                        w_shard.to(device), sw_shard.to(device), mode=mode)
+            layer = ColumnShardedLinear(plan, w_shard.to(device), sw_shard.to(device), mode=mode)
             for s in layer._sets:
                 s["gathered"].fill_(float("nan"))
             layer.gathered.fill_(float("nan"))
