@@ -908,12 +908,14 @@ int ci8_channel_gemv(const void* x, const int8_t* w, const void* w_scale, void* 
   if (aligned(x, 16) && n >= 2048) {
     // production path: TMA-staged weights, one CTA per slab of channels, one wave
     const int sms = sm_count();
-    int slab = ((n + sms - 1) / sms + 15) / 16 * 16;   // a consumer warp owns 16 channels
+    // slabs in steps of 16 channels, one MMA fragment (a warp of the 9..16-row form, which owns 32, may end
+    // up with only its first 16 in use)
+    int slab = ((n + sms - 1) / sms + 15) / 16 * 16;
     if (slab < 16) slab = 16;
-    if (slab > GemvTmaConfig::kMaxSlab) slab = GemvTmaConfig::kMaxSlab;
+    if (slab > GemvTmaConfig<1>::kMaxSlab) slab = GemvTmaConfig<1>::kMaxSlab;
     static std::atomic<uint64_t> smem_done1{0}, smem_done2{0};
-    cudaError_t err = m <= 8 ? ensure_smem(gemv_w8a16_tma_kernel<1>, GemvTmaConfig::kSmemBytes, smem_done1)
-                             : ensure_smem(gemv_w8a16_tma_kernel<2>, GemvTmaConfig::kSmemBytes, smem_done2);
+    cudaError_t err = m <= 8 ? ensure_smem(gemv_w8a16_tma_kernel<1>, GemvTmaConfig<1>::kSmemBytes, smem_done1)
+                             : ensure_smem(gemv_w8a16_tma_kernel<2>, GemvTmaConfig<2>::kSmemBytes, smem_done2);
     if (err != cudaSuccess) return err;
     CUtensorMap map_w, map_x;
     err = make_map(&map_w, w, n, k, slab);
@@ -924,10 +926,10 @@ int ci8_channel_gemv(const void* x, const int8_t* w, const void* w_scale, void* 
     const auto* sb = static_cast<const __nv_bfloat16*>(w_scale);
     auto* ob = static_cast<__nv_bfloat16*>(out);
     if (m <= 8)
-      return launch_serialized(gemv_w8a16_tma_kernel<1>, ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s,
+      return launch_serialized(gemv_w8a16_tma_kernel<1>, ctas, GemvTmaConfig<1>::kThreads, GemvTmaConfig<1>::kSmemBytes, s,
                                map_w, map_x, sb, ob, m, n, k, slab);
     else
-      return launch_serialized(gemv_w8a16_tma_kernel<2>, ctas, GemvTmaConfig::kThreads, GemvTmaConfig::kSmemBytes, s,
+      return launch_serialized(gemv_w8a16_tma_kernel<2>, ctas, GemvTmaConfig<2>::kThreads, GemvTmaConfig<2>::kSmemBytes, s,
                                map_w, map_x, sb, ob, m, n, k, slab);
     return cudaGetLastError();
   }

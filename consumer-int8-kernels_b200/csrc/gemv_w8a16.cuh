@@ -224,6 +224,7 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const int8_t* __restr
 // each K block rides in the same stage (two swizzled TMA boxes) and is read with conflict-free
 // 8-byte shared loads. HBM only sees the weights, once,
 // through deep asynchronous copies instead of register-fed loads.
+template <int kRowBlocksT = 1>
 struct GemvTmaConfig {
   static constexpr int kBlockK = 128;
   static constexpr int kMaxSlab = 256;
@@ -231,11 +232,13 @@ struct GemvTmaConfig {
   static constexpr int kXBoxBytes = 16 * 128;               // 16 activation rows x 64 BF16
   static constexpr int kStageBytes = kWeightBytes + 2 * kXBoxBytes;   // + the 128 K positions of x
   static constexpr int kStages = 6;
-  // sixteen consumer warps of 16 channels each: four per scheduler, so that one warp's shared-memory and
-  // conversion latencies are covered by the others (eight warps of 32 channels left the issue slots
-  // half empty while the kernel was still 25 % short of the weight stream's rate)
-  static constexpr int kConsumerWarps = 16;
-  static constexpr int kGroups = 1;            // 16-channel groups (A fragments) per consumer warp
+  // Up to 8 activation rows: sixteen consumer warps of 16 channels each, four per scheduler, so that one warp's
+  // shared-memory and conversion latencies are covered by the others (eight warps of 32 channels left the issue
+  // slots half empty while the kernel was still 25 % short of the weight stream's rate: 35.8 -> 33.1 us).
+  // 9..16 rows: eight warps of 32 channels, which read each activation fragment once for two channel groups
+  // (with sixteen warps the doubled fragment loads took back what the extra warps gave).
+  static constexpr int kConsumerWarps = kRowBlocksT == 1 ? 16 : 8;
+  static constexpr int kGroups = kRowBlocksT == 1 ? 1 : 2;   // 16-channel groups (A fragments) per consumer warp
   static constexpr int kThreads = (1 + kConsumerWarps) * 32;
   static constexpr int kSmemBytes = kStages * kStageBytes + 256 + 1024;
 };
@@ -253,11 +256,11 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
 
 // map_x: BF16 activations [m, k] as boxes of 64 columns x 16 rows (rows past m read as zero).
 template <int kRowBlocks>
-__global__ void __launch_bounds__(GemvTmaConfig::kThreads, 1)
+__global__ void __launch_bounds__(GemvTmaConfig<kRowBlocks>::kThreads, 1)
 gemv_w8a16_tma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       const __nv_bfloat16* __restrict__ sw, __nv_bfloat16* __restrict__ out,
                       int m, int n, int k, int slab) {
-  using Cfg = GemvTmaConfig;
+  using Cfg = GemvTmaConfig<kRowBlocks>;
   extern __shared__ uint8_t gemv_tma_smem[];
   const uint32_t raw_addr = smem_u32(gemv_tma_smem);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
