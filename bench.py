@@ -16,7 +16,7 @@ GPU, the all-gather of the BF16 output). Workloads (shapes of the five benchmark
 the public operators with host buffers (pinned host -> device copy of the activations and
 device -> host copy of the result inside the timed region). ``--impl reference`` times the
 reference's own host restatement of the path (torch on the CPU), on the whole workload when that
-fits the time budget and on a bounded row sample otherwise.
+ends within a few minutes and on a bounded row sample otherwise.
 Before anything is timed, a seeded sample of rows of the result on EVERY rank is compared bit for bit
 with the CPU checker (the reference's discipline: benchmarks/microbench.py:206-214 asserts equality
 before it times); a mismatch ends the run with a non-zero exit code, and the line carries
@@ -45,6 +45,7 @@ WORKLOADS = {
     "prefill_down": dict(m=4096, k=17408, n=5120, config="configs[2]"),
     "grouped": dict(m=2048, k=32768, n=7168, groups=8, config="configs[3]"),
     "decode": dict(m=16, k=5120, n=34816, config="configs[1]"),
+    "decode_m8": dict(m=8, k=5120, n=34816, config="configs[1], M=8 (profile-only: the 8-row forms of the decode kernels)"),
     "q8_block": dict(m=4096, k=4096, n=1024, config="block-32 Q8_0 (the reference's benchmark shape)"),
     # the sharded output with next to no arithmetic (K = 32): what is left is the epilogue's tile stores,
     # i.e. on several GPUs the peer-store bandwidth of the fused gather
@@ -375,11 +376,15 @@ def run_ours(args, spec, rank, world, local_rank):
     tensor_peak = burst_peak if region_s < 1.0 else sustained_peak
     gemm_tops = 2.0 * m * plan.shard_n * k / (gemm_ms * 1e-3) / 1e12
     traffic = KERNEL_TRAFFIC.get(args.workload if world == 1 else f"{args.workload}/{world}")
-    algorithmic = float(m * k + plan.shard_n * k + 2 * m * plan.shard_n + 4 * m + 2 * plan.shard_n)
+    # per GPU: the codes, this rank's weights and scales, and the BF16 result: its own block written once and,
+    # on several GPUs, the other ranks' blocks arriving over NVLink (the whole [M, N] lands in every GPU's memory)
+    algorithmic = float(m * k + plan.shard_n * k + 2 * m * n + 4 * m + 2 * plan.shard_n)
+    # captures of the shard-shaped GEMM are taken on one GPU; the peers' blocks are added by construction
+    traffic_bytes = (traffic["read"] + traffic["write"] + (plan.gather_bytes_received if world > 1 else 0)) if traffic else None
     roofline = dict(bound="tensor", achieved=gemm_tops, peak=tensor_peak, unit="TFLOP/s", frac=gemm_tops / tensor_peak,
                     frac_sustained=gemm_tops / sustained_peak, frac_nominal=gemm_tops / 4500.0,
-                    traffic=traffic["read"] + traffic["write"] if traffic else None,
-                    traffic_ratio=(traffic["read"] + traffic["write"]) / algorithmic if traffic else None,
+                    traffic=traffic_bytes,
+                    traffic_ratio=traffic_bytes / algorithmic if traffic else None,
                     traffic_source=traffic["source"] if traffic else None, kernel_source=source_tag(),
                     kernel="gemm_i8_kernel<2,fused>",
                     note=f"integer ops 2*M*N*K per launch / CUDA-event launch time ({gemm_ms:.3f} ms, per GPU); peak = 2 x "
@@ -431,6 +436,11 @@ KERNEL_TRAFFIC = {
     "sharded": dict(read=676.3e6, write=1107.6e6, source="2e7a52a65e28", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
     "prefill_gate_up": dict(read=199.5e6, write=247.7e6, source="2e7a52a65e28", profile="profiles/gemm_i8_kernel_prefill_gate_up.md"),
     "prefill_down": dict(read=381.4e6, write=32.1e6, source="2e7a52a65e28", profile="profiles/gemm_i8_kernel_prefill_down.md"),
+    # one rank's channel shard of the sharded workload, captured on one GPU (--shard-of G): its own reads and the
+    # writes of its own block; run_ours adds the peers' blocks that arrive over NVLink
+    "sharded/2": dict(read=373.8e6, write=535.8e6, source="2e7a52a65e28", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
+    "sharded/4": dict(read=227.2e6, write=250.2e6, source="2e7a52a65e28", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
+    "sharded/8": dict(read=152.1e6, write=105.7e6, source="2e7a52a65e28", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
 }
 
 
@@ -647,6 +657,7 @@ def profile_only(args, spec):
 
     device = torch.device("cuda", 0)
     m, n, k = spec["m"], spec["n"], spec["k"]
+    n //= args.shard_of       # one rank's channel shard of the workload, run on this one GPU
     if args.workload == "q8_block":
         import ctypes
         gen = torch.Generator().manual_seed(0)
@@ -673,14 +684,15 @@ def profile_only(args, spec):
     else:
         inputs = workloads.linear_inputs(m, n, k, seed=0)
         x, sw = inputs.x.to(device), inputs.w_scale.to(device)
-        copies = [inputs.w.to(device) for _ in range(3 if args.workload == "decode" else 1)]
+        decode = args.workload in ("decode", "decode_m8")
+        copies = [inputs.w.to(device) for _ in range(3 if decode else 1)]
         codes = torch.empty(m, k, dtype=torch.int8, device=device)
         scales = torch.empty(m, device=device)
         out = torch.empty(m, n, dtype=torch.bfloat16, device=device)
         for i in range(args.steps):
             ops.quantize_rows(x, codes, scales)
             ops.fused_channel_mm(codes, copies[i % len(copies)], scales, sw, out, args.schedule)
-            if args.workload == "decode":
+            if decode:
                 ops.channel_gemv(x, copies[i % len(copies)], sw, out)
                 ops.dynamic_channel_mm(x, copies[i % len(copies)], sw, codes, scales, out)
     torch.cuda.synchronize()
@@ -705,6 +717,9 @@ def main():
     parser.add_argument("--workload", choices=list(WORKLOADS), default="sharded")
     parser.add_argument("--profile-only", action="store_true",
                         help="run --steps launches of the workload's kernels with no timing (for ncu captures)")
+    parser.add_argument("--shard-of", type=int, default=1, choices=[1, 2, 4, 8],
+                        help="--profile-only: run one rank's N/G channel shard of the workload (for DRAM-traffic captures "
+                             "of the per-GPU GEMM of the sharded runs)")
     parser.add_argument("--schedule", type=int, default=0)
     parser.add_argument("--gather", choices=["fused", "fused_flag", "fused_nccl_barrier", "nccl"], default="fused",
                         help="N>1: peer stores from the GEMM epilogue (closed inside the kernel, or by an NCCL "
@@ -725,7 +740,7 @@ def main():
     if args.profile_only:
         profile_only(args, spec)
         return
-    if args.workload in ("decode", "grouped", "q8_block"):
+    if args.workload in ("decode", "decode_m8", "grouped", "q8_block"):
         raise SystemExit("the decode, grouped and q8_block workloads are timed inside the default run (other_configs) "
                          "or launched with --profile-only")
     if world != args.gpus:

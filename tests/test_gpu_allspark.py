@@ -66,3 +66,55 @@ def test_unpack_rejects_wrong_geometry(ops):
     with pytest.raises(RuntimeError, match="AllSpark N32K16"):
         ops.unpack_allspark(packed, packed_scales, torch.empty(24, 32, dtype=torch.int8, device=DEV),
                             torch.empty(24, dtype=torch.bfloat16, device=DEV))
+
+
+def _vllm_packer():
+    """vLLM's own AllSpark packer, which is what the reference's test packs with
+    (tests/test_cuda_ops.py:440-471). Skips when the installed vLLM cannot run it on this GPU."""
+    try:
+        from vllm import _custom_ops as vops
+    except Exception as error:          # vLLM absent or its extension does not load
+        pytest.skip(f"vLLM is not importable here: {type(error).__name__}")
+    try:
+        probe = torch.zeros(32, 16, dtype=torch.uint8, device=DEV)
+        vops.allspark_repack_weight(probe.T.contiguous(), torch.ones(1, 32, dtype=torch.bfloat16, device=DEV), None, False)
+        torch.cuda.synchronize()
+        torch.zeros(1, device=DEV).add_(1)      # a launch error of the call above ("no kernel image") surfaces here
+        torch.cuda.synchronize()
+    except Exception as error:          # the operator is missing, or was not built for this architecture
+        pytest.skip(f"vLLM's allspark_repack_weight does not run here: {type(error).__name__}: {str(error)[:120]}")
+    return vops.allspark_repack_weight
+
+
+@pytest.mark.parametrize("n,k", [(16, 16), (48, 80), (128, 512), (5120, 3072)])
+def test_allspark_unpack_inverts_vllms_own_packer(ops, n, k):
+    """The reference's test, with the reference's packer: codes and scales packed by vLLM's
+    allspark_repack_weight come back bit for bit, from a captured graph, twice, on repacked inputs."""
+    repack = _vllm_packer()
+    generator = torch.Generator(device=DEV).manual_seed(319)
+    codes = torch.randint(0, 256, (n, k), device=DEV, dtype=torch.uint8, generator=generator)
+    scales = torch.randn(n, device=DEV, dtype=torch.bfloat16, generator=generator)
+    packed, packed_scales, _ = repack(codes.T.contiguous(), scales[None], None, False)
+    packed_scales = packed_scales.flatten()
+    restored = torch.empty_like(codes, dtype=torch.int8)
+    restored_scales = torch.empty_like(scales)
+    ops.unpack_allspark(packed, packed_scales, restored, restored_scales)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ops.unpack_allspark(packed, packed_scales, restored, restored_scales)
+    for _ in range(2):
+        restored.zero_()
+        restored_scales.zero_()
+        graph.replay()
+        torch.testing.assert_close(restored, (codes.short() - 128).char(), atol=0, rtol=0)
+        torch.testing.assert_close(restored_scales, scales, atol=0, rtol=0)
+        # the CPU checker and its packer agree with vLLM's layout as well
+        want_packed, want_packed_scales = ref.pack_allspark_ref(codes.cpu(), scales.cpu())
+        if n % 32 == 0:      # (with padding rows the two packers may fill the padding differently)
+            assert torch.equal(packed.cpu().reshape(-1), want_packed.reshape(-1)), "the checker's packer and vLLM's differ"
+            assert torch.equal(packed_scales.cpu().view(torch.int16), want_packed_scales.view(torch.int16))
+        codes.bitwise_xor_(255)
+        scales.neg_()
+        changed, changed_scales, _ = repack(codes.T.contiguous(), scales[None], None, False)
+        packed.copy_(changed)
+        packed_scales.copy_(changed_scales.flatten())

@@ -92,7 +92,15 @@ def _rank_main(rank, world, port, chunks, fail_rank, results):
         gathered = layer.forward(inputs.x)
         codes, scales = ref.quantize_rows_ref(inputs.x)
         _, want = ref.fused_channel_mm_ref(codes, inputs.w, scales, inputs.w_scale)
-        results[rank] = bool(torch.equal(plan.row_major(gathered), want))
+        ok = bool(torch.equal(plan.row_major(gathered), want))
+        # the column-sharded mode: no collective at all, every rank keeps its own [M, N/G] block
+        if chunks == 1:
+            alone = ColumnShardedLinear(plan, w_shard, sw_shard, operators=_checker_operators(), mode="none")
+            block = alone.forward(inputs.x)[0, rank]
+            ok = ok and bool(torch.equal(block, want[:, plan.channels]))
+        with pytest.raises(ValueError, match="mode must be"):
+            ColumnShardedLinear(plan, w_shard, sw_shard, operators=_checker_operators(), mode="ring")
+        results[rank] = ok
     finally:
         dist.destroy_process_group()
 
