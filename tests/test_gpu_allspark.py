@@ -68,21 +68,37 @@ def test_unpack_rejects_wrong_geometry(ops):
                             torch.empty(24, dtype=torch.bfloat16, device=DEV))
 
 
+_VLLM_PROBE = """
+import torch
+from vllm import _custom_ops as vops
+probe = torch.zeros(32, 16, dtype=torch.uint8, device="cuda")
+vops.allspark_repack_weight(probe.T.contiguous(), torch.ones(1, 32, dtype=torch.bfloat16, device="cuda"), None, False)
+torch.cuda.synchronize()
+torch.zeros(1, device="cuda").add_(1)   # a launch error of the call above ("no kernel image") surfaces here
+torch.cuda.synchronize()
+"""
+_vllm_verdict = None
+
+
 def _vllm_packer():
     """vLLM's own AllSpark packer, which is what the reference's test packs with
-    (tests/test_cuda_ops.py:440-471). Skips when the installed vLLM cannot run it on this GPU."""
-    try:
-        from vllm import _custom_ops as vops
-    except Exception as error:          # vLLM absent or its extension does not load
-        pytest.skip(f"vLLM is not importable here: {type(error).__name__}")
-    try:
-        probe = torch.zeros(32, 16, dtype=torch.uint8, device=DEV)
-        vops.allspark_repack_weight(probe.T.contiguous(), torch.ones(1, 32, dtype=torch.bfloat16, device=DEV), None, False)
-        torch.cuda.synchronize()
-        torch.zeros(1, device=DEV).add_(1)      # a launch error of the call above ("no kernel image") surfaces here
-        torch.cuda.synchronize()
-    except Exception as error:          # the operator is missing, or was not built for this architecture
-        pytest.skip(f"vLLM's allspark_repack_weight does not run here: {type(error).__name__}: {str(error)[:120]}")
+    (tests/test_cuda_ops.py:440-471). Whether the installed vLLM can run it on this GPU is found out in a
+    child process, once, so that a failing launch cannot touch this process; the test skips if it cannot."""
+    global _vllm_verdict
+    if _vllm_verdict is None:
+        import subprocess
+        import sys
+
+        try:
+            child = subprocess.run([sys.executable, "-c", _VLLM_PROBE], capture_output=True, text=True, timeout=300)
+            lines = [line.strip() for line in (child.stderr or "").splitlines() if "error" in line.lower()]
+            _vllm_verdict = "ok" if child.returncode == 0 else (lines[0][:160] if lines else f"exit code {child.returncode}")
+        except Exception as error:
+            _vllm_verdict = f"{type(error).__name__}"
+    if _vllm_verdict != "ok":
+        pytest.skip(f"vLLM's allspark_repack_weight does not run here: {_vllm_verdict}")
+    from vllm import _custom_ops as vops
+
     return vops.allspark_repack_weight
 
 
