@@ -15,7 +15,9 @@
 // ~200 cycles, draining their accumulators ~1700), which is inherent to per-block FP32 rescaling
 // of INT32 partials — the block-scaled tcgen05 kinds take floating-point operands only. (Replacing
 // the conversion instruction by an integer add and a packed FP32 subtract of 1.5 * 2^23 was
-// measured slower.)
+// measured slower; so was letting the MMA do the add: accumulators pre-set to the bits of 1.5 * 2^23
+// with tcgen05.st after every read, MMA accumulating onto them, one packed subtract per two values:
+// bit-exact, 143 us against 123 us on M=4096, N=1024, K=4096.)
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
