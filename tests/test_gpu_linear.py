@@ -184,7 +184,9 @@ def test_channel_mm_biased_weights_on_the_tensor_core_path(ops, m, n, k):
     check()
 
 
-@pytest.mark.parametrize("m,n,k", [(17, 128, 512), (200, 132, 544), (1041, 260, 1056), (16, 132, 544), (3, 4, 32)])
+@pytest.mark.parametrize("m,n,k", [(17, 128, 512), (200, 132, 544), (1041, 260, 1056), (16, 132, 544), (3, 4, 32),
+                                   # 65..128 rows: the one-CTA tile with its INT32 tile stores; a pitch that rules them out
+                                   (100, 260, 160), (128, 512, 256), (90, 1000, 96), (300, 1004, 96)])
 def test_cutlass_channel_mm_writes_exact_accumulators(ops, m, n, k):
     a, w, sa, sw = linear_case(m, n, k, seed=m * n)
     out, check_out = guarded((m, n), torch.bfloat16, float("nan"))
