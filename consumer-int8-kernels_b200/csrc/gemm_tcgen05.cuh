@@ -71,13 +71,18 @@ struct GemmParams {
                               // tile_n + 32 columns wide, the others tile_n (0: all tiles are tile_n wide)
   // Grouped form with a caller workspace: every tile of the last, partial wave is cut ALONG THE GROUPS
   // into `groups` pieces that run on as many CTA pairs at once (piece_items = leftover tiles x groups
-  // work items behind the whole tiles). A piece writes its group's FP32 terms fmul(float(acc_g), sa_g)
+  // work items behind the whole tiles, drawn from a counter by the pairs that finish their whole tiles first). A piece writes its group's FP32 terms fmul(float(acc_g), sa_g)
   // to `terms`; when all pieces of a tile have arrived (piece_sync) each of them adds the terms of its
   // share of the tile in ascending group order (the same fadd chain as one CTA would run) and stores it.
   int piece_items;
   float* terms;               // [leftover tile][group][256 rows][256 columns]
-  unsigned* piece_sync;       // [leftover tile][2]: pieces' warps arrived / departed; zero before and after
+  unsigned* piece_sync;       // [leftover tile][2]: pieces' warps arrived / departed, and word kPieceFetchWord:
+                              // pieces drawn so far; all zero before and after a launch
 };
+
+// Word of the pieces' header (piece_sync) that counts the draws of a launch; the words before it are the
+// arrival and departure counters of the leftover tiles (two each, at most 37 tiles on 74 workers).
+constexpr int kPieceFetchWord = 192;
 
 // Grouped form: item -> the tile index tile_coords takes, the groups [g_begin, g_end) the item covers
 // and, for a piece, the index of its tile among the leftover tiles (-1 for a whole tile).
@@ -132,7 +137,14 @@ struct GemmConfig {
   // (the workspace form gives one ring stage to the staging boxes of its INT32 tile stores)
   static constexpr int kStages = (kCtas == 1 ? 4 : 6) - (kMode == kModeWorkspace ? 1 : 0);
   static constexpr int kEpiWarps = kMode == kModeGrouped ? 8 : 4;
-  static constexpr int kThreads = (2 + kEpiWarps) * 32;
+  // Warp 0 loads, warp 1 issues the MMAs, the epilogue warps follow. The grouped form keeps 128 FP32 running
+  // sums per epilogue thread: its epilogue warps start at warp 4 (warps 2 and 3 idle), so that the first
+  // warpgroup can hand most of its registers to the two epilogue warpgroups (setmaxnreg); with ten warps
+  // one scheduler would hold three of them, 168 registers each, and the sums would spill.
+  static constexpr int kFirstEpiWarp = kMode == kModeGrouped ? 4 : 2;
+  static constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
+  // 384 threads start with 168 registers each; 128 x 40 + 256 x 232 is the same pool
+  static constexpr int kRegsFrontWarps = 40, kRegsEpiWarps = 232;
   static constexpr int kColsPerEpiWarp = kTileN / (kEpiWarps / 4);
   static constexpr int kStoreBoxBytes = 32 * 128;     // one staged store box: 32 rows x 64 BF16
   static constexpr int kStoreBufs = kEpiWarps == 4 ? 2 : 1;   // staging boxes per epilogue warp
@@ -197,6 +209,14 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Grouped form, the pieces' workspace. One group's FP32 terms of one 256 x 256 tile are a plane of 16384
+// float4, cut into blocks of 32 rows x 32 columns (row blocks outer): inside a block the eight float4 of a
+// row's 32 columns are spread with the row (the lane) as the fastest index, so that a warp whose lanes hold
+// one row each writes, and later reads, 512 contiguous bytes per instruction.
+__device__ __forceinline__ int piece_term_index(int row_block, int col_block, int quad, int lane) {
+  return ((row_block * 8 + col_block) * 8 + quad) * 32 + lane;
+}
+
 // Grouped form, end of a piece: the warp reports its terms, waits until every warp of every piece of the
 // tile has done so, then adds the terms of this piece's share of the tile in ascending group order
 // and stores it.
@@ -227,60 +247,100 @@ __device__ __forceinline__ void finish_piece(float* terms, unsigned* piece_sync,
   }
   all_in = __shfl_sync(0xffffffffu, all_in, 0);
   if (all_in) {
-    // Share of piece g_begin: vectors of 8 columns [begin, end) of the tile's 256 x 32 vectors, walked by
-    // the epilogue threads of both CTAs. Ascending-group fadd chain, then the channel scale.
-    constexpr int kTileRows = Cfg::kBlockM * kCtas, kVectors = kTileRows * (Cfg::kTileN / 8);
-    const int begin = static_cast<int>(static_cast<long long>(kVectors) * g_begin / p.groups);
-    const int end = static_cast<int>(static_cast<long long>(kVectors) * (g_begin + 1) / p.groups);
-    const int me = static_cast<int>(rank) * (Cfg::kEpiWarps * 32) + epi * 32 + lane;
-    const float* tile_terms = p.terms + static_cast<size_t>(leftover) * p.groups * kTileRows * Cfg::kTileN;
+    // Share of piece g_begin: units [begin, end) of the plane's 256 units (a unit: the 32 rows of a block x
+    // 8 columns, i.e. two adjacent float4 per lane), walked by the epilogue warps of both CTAs. Ascending-
+    // group fadd chain, then the channel scale.
+    constexpr int kTileRows = Cfg::kBlockM * kCtas, kPlane = kTileRows * Cfg::kTileN / 4, kUnits = kPlane / 64;
+    const int begin = static_cast<int>(static_cast<long long>(kUnits) * g_begin / p.groups);
+    const int end = static_cast<int>(static_cast<long long>(kUnits) * (g_begin + 1) / p.groups);
+    const float4* tile_terms = reinterpret_cast<const float4*>(p.terms) + static_cast<size_t>(leftover) * p.groups * kPlane;
     const int tile_row0 = mt * kTileRows;
-    for (int v = begin + me; v < end; v += kCtas * Cfg::kEpiWarps * 32) {
-      const int tile_row = v / (Cfg::kTileN / 8), col8 = (v % (Cfg::kTileN / 8)) * 8;
-      const int out_row = tile_row0 + tile_row, col = n0 + col8;
-      if (out_row >= p.m || col >= p.n || col8 >= n_width) continue;
-      const float* src = tile_terms + static_cast<size_t>(tile_row) * Cfg::kTileN + col8;
-      float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
-      // four groups' terms are fetched together (one round trip to L2 for four), then added in ascending order
-#pragma unroll 1
-      for (int g0 = 0; g0 < p.groups; g0 += 4) {
-        float4 a[4], b[4];
+    const bool sw_vec = reinterpret_cast<uintptr_t>(p.sw) % 16 == 0;
+    // Two units per round, all of their loads in flight together: with eight groups a warp's whole share
+    // (two units) costs one round trip to L2.
+    constexpr int kStep = kCtas * Cfg::kEpiWarps;
+    for (int unit0 = begin + rank * Cfg::kEpiWarps + epi; unit0 < end; unit0 += 2 * kStep) {
+      int col[2], out_row[2];
+      bool live[2];
+      const float4* src[2];
+      uint4 sw_words[2];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          if (g0 + i < p.groups) {
-            const float4* at = reinterpret_cast<const float4*>(src + static_cast<size_t>(g0 + i) * kTileRows * Cfg::kTileN);
-            a[i] = __ldcg(at);
-            b[i] = __ldcg(at + 1);
+      for (int u = 0; u < 2; ++u) {
+        const int unit = unit0 + u * kStep;
+        const int block = unit >> 2, pair = unit & 3;
+        const int row_block = block >> 3, col_block = block & 7;
+        const int col8 = col_block * 32 + pair * 8;
+        out_row[u] = tile_row0 + row_block * 32 + lane;
+        col[u] = n0 + col8;
+        live[u] = unit < end && col[u] < p.n && col8 < n_width;      // the same for every lane
+        src[u] = tile_terms + piece_term_index(row_block, col_block, 2 * pair, lane);
+        // the eight channel scales of the unit (the same for every lane), fetched ahead of the terms
+        sw_words[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (live[u]) {
+          if (sw_vec && col[u] + 8 <= p.n) {
+            sw_words[u] = __ldg(reinterpret_cast<const uint4*>(p.sw + col[u]));
+          } else {
+            uint16_t* parts = reinterpret_cast<uint16_t*>(&sw_words[u]);
+            for (int j = 0; j < 8; ++j)
+              if (col[u] + j < p.n) parts[j] = reinterpret_cast<const uint16_t*>(p.sw)[col[u] + j];
+          }
+        }
+      }
+      float4 lo[2], hi[2];
+      // eight groups' terms of both units are fetched together, then added in ascending group order
+#pragma unroll 1
+      for (int g0 = 0; g0 < p.groups; g0 += 8) {
+        float4 a[2][8], b[2][8];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const float4* base = src[u] + static_cast<size_t>(g0) * kPlane;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (live[u] && g0 + i < p.groups) {
+              a[u][i] = __ldcg(base + i * kPlane);
+              b[u][i] = __ldcg(base + i * kPlane + 32);
+            }
           }
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          if (g0 + i < p.groups) {
-            if (g0 + i == 0) {
-              lo = a[i];
-              hi = b[i];
-            } else {
-              lo = make_float4(__fadd_rn(lo.x, a[i].x), __fadd_rn(lo.y, a[i].y), __fadd_rn(lo.z, a[i].z), __fadd_rn(lo.w, a[i].w));
-              hi = make_float4(__fadd_rn(hi.x, b[i].x), __fadd_rn(hi.y, b[i].y), __fadd_rn(hi.z, b[i].z), __fadd_rn(hi.w, b[i].w));
+        for (int u = 0; u < 2; ++u) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (live[u] && g0 + i < p.groups) {
+              if (g0 + i == 0) {
+                lo[u] = a[u][i];
+                hi[u] = b[u][i];
+              } else {
+                lo[u] = make_float4(__fadd_rn(lo[u].x, a[u][i].x), __fadd_rn(lo[u].y, a[u][i].y), __fadd_rn(lo[u].z, a[u][i].z),
+                                    __fadd_rn(lo[u].w, a[u][i].w));
+                hi[u] = make_float4(__fadd_rn(hi[u].x, b[u][i].x), __fadd_rn(hi[u].y, b[u][i].y), __fadd_rn(hi[u].z, b[u][i].z),
+                                    __fadd_rn(hi[u].w, b[u][i].w));
+              }
             }
           }
         }
       }
-      const float sum[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-      uint32_t words[4];
 #pragma unroll
-      for (int j = 0; j < 8; j += 2) {
-        const float s0 = col + j < p.n ? __bfloat162float(p.sw[col + j]) : 0.f;
-        const float s1 = col + j + 1 < p.n ? __bfloat162float(p.sw[col + j + 1]) : 0.f;
-        words[j >> 1] = pack_bf16x2(__fmul_rn(sum[j], s0), __fmul_rn(sum[j + 1], s1));
-      }
-      __nv_bfloat16* dst = p.out + static_cast<size_t>(out_row) * p.n + col;
-      if (out_vec && col + 8 <= p.n) {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(words[0], words[1], words[2], words[3]);
-      } else {
-        for (int j = 0; j < 8; ++j)
-          if (col + j < p.n)
-            reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>((j & 1) ? (words[j >> 1] >> 16) : (words[j >> 1] & 0xffffu));
+      for (int u = 0; u < 2; ++u) {
+        if (!live[u] || out_row[u] >= p.m) continue;
+        const float sum[8] = {lo[u].x, lo[u].y, lo[u].z, lo[u].w, hi[u].x, hi[u].y, hi[u].z, hi[u].w};
+        const uint32_t sw_pairs[4] = {sw_words[u].x, sw_words[u].y, sw_words[u].z, sw_words[u].w};
+        uint32_t words[4];
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          // a BF16 is the upper half of the FP32 with the same value
+          const float s0 = __uint_as_float(sw_pairs[j >> 1] << 16);
+          const float s1 = __uint_as_float(sw_pairs[j >> 1] & 0xffff0000u);
+          words[j >> 1] = pack_bf16x2(__fmul_rn(sum[j], s0), __fmul_rn(sum[j + 1], s1));
+        }
+        __nv_bfloat16* dst = p.out + static_cast<size_t>(out_row[u]) * p.n + col[u];
+        if (out_vec && col[u] + 8 <= p.n) {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(words[0], words[1], words[2], words[3]);
+        } else {
+          for (int j = 0; j < 8; ++j)
+            if (col[u] + j < p.n)
+              reinterpret_cast<uint16_t*>(dst)[j] = static_cast<uint16_t>((j & 1) ? (words[j >> 1] >> 16) : (words[j >> 1] & 0xffffu));
+        }
       }
     }
   }
@@ -315,6 +375,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   auto tmem_empty_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + 2 + b); };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_region + 8 * (2 * Cfg::kStages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // grouped form with pieces: the barrier the piece's number is announced on, and the number
+  const uint32_t piece_bar = bar_base + 8u * (2 * Cfg::kStages + 5);
+  volatile int* piece_slot = reinterpret_cast<volatile int*>(bar_region + 8 * (2 * Cfg::kStages + 6));
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
@@ -329,6 +392,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(tmem_full_bar(b), 1);
       mbar_init(tmem_empty_bar(b), Cfg::kEpiWarps * kCtas);
     }
+    if constexpr (kMode == kModeGrouped) mbar_init(piece_bar, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -372,116 +436,171 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   const unsigned long long calls_done = out_maps.state ? ld_relaxed_u64(out_maps.state) : 0ull;
 
   const int num_kb = (p.k + Cfg::kBlockK - 1) / Cfg::kBlockK;   // per group
-  const int total_tiles = p.total_items;   // work items: whole tiles, then column slices
+  // Work items: whole tiles, then column slices, walked with a fixed stride. The pieces of the grouped form
+  // are not dealt out in advance: a worker that has finished its whole tiles takes the next piece from a
+  // counter, so the pieces go to the workers that are ahead. (SM clocks differ by a few percent between
+  // parts of the chip under the power cap; with a fixed assignment the pieces of a tile, which have to wait
+  // for one another, finished with the slowest worker that held one.)
+  const bool pieces = kMode == kModeGrouped && p.piece_items > 0;
+  const int total_tiles = pieces ? p.full_tiles : p.total_items;
+  // Called by whole warps once their fixed items are done. The first CTA's load warp draws the number and
+  // announces it to every other role of the CTA (pair); returns the item, or -1 when no piece is left.
+  auto fetch_piece = [&]() -> int {
+    if constexpr (kMode != kModeGrouped) {
+      return -1;
+    } else {
+      if (!pieces) return -1;
+      int q = 0;
+      if (warp == 0 && rank == 0) {
+        if (lane == 0) {
+          const unsigned workers = gridDim.x / kCtas;
+          q = static_cast<int>(atomicAdd(p.piece_sync + kPieceFetchWord, 1u));
+          // every worker draws exactly once per launch: the last draw puts the counter back for the next one
+          if (static_cast<unsigned>(q) == workers - 1u) p.piece_sync[kPieceFetchWord] = 0u;
+          *piece_slot = q;
+          if constexpr (kCtas == 2)
+            st_shared_cluster_u32(map_to_cta(smem_u32(const_cast<int*>(piece_slot)), 1), static_cast<uint32_t>(q));
+          mbar_arrive(piece_bar);
+          if constexpr (kCtas == 2) mbar_arrive_cluster(piece_bar, 1);
+        }
+        q = __shfl_sync(0xffffffffu, q, 0);
+      } else {
+        if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(piece_bar, 0u, abort_flag))) return -1;
+        q = *piece_slot;
+      }
+      return q < p.piece_items ? p.full_tiles + q : -1;
+    }
+  };
   const int first_tile = kCtas == 2 ? (blockIdx.x >> 1) : blockIdx.x;
   const int tile_stride = kCtas == 2 ? (gridDim.x >> 1) : gridDim.x;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    // The producer and MMA loops are run by their whole warp with one elected lane issuing: the
-    // loop state then lives in uniform registers, which is where TMA and MMA instructions take
-    // their operands. Issued from a single thread inside a divergent branch, every instruction
-    // pays tens of cycles of register moves (measured: 47-76 cycles per MMA against 128 cycles
-    // of tensor-pipe time for a 128 x 256 x 32 step, before the waits and commits).
-    int stage = 0;
-    uint32_t phase = 0;
-    const uint32_t leader_full0 = kCtas == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
-    // the raster keeps a group of A rows in L2 while the weights stream past: A lines leave L2 last
-    const uint64_t a_policy = l2_policy_evict_last();
-    bool ok = true;
-    for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
-      int mt, nt, n_start, n_width, g_begin = 0, g_end = p.groups, leftover = -1, tile_index = tile;
-      bool alt;
-      if constexpr (kMode == kModeGrouped) grouped_item(p, tile, tile_index, g_begin, g_end, leftover);
-      tile_coords(p, tile_index, mt, nt, n_start, n_width, alt);
-      const int a_row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM;
-      // a pair's CTAs supply half the weight rows each; slices and wide tiles load through their own box
-      // (biased pair: the first CTA loads 128 channels through map_w, the second 120 through the other map)
-      const int w_row = n_start + rank * (kMode == kModeBiased ? Cfg::kBRowsSmem : n_width / kCtas);
-      const CUtensorMap* w_map = (alt || (kMode == kModeBiased && rank == 1)) ? &map_w_slice : &map_w;
-      const uint32_t tx = kMode == kModeBiased
-                              ? static_cast<uint32_t>(kCtas * Cfg::kABytes + Cfg::kChannelsPerTile * Cfg::kBlockK)
-                              : static_cast<uint32_t>(alt ? p.stage_tx_slice : p.stage_tx) * kCtas;
-      for (int g = g_begin; ok && g < g_end; ++g) {
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) { ok = false; break; }
-          if (elect_one()) {
-            if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), tx);
-            const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
-            const uint32_t b_dst = a_dst + Cfg::kABytes;
-            const uint32_t bar = leader_full0 + 8u * stage;
-            const int kx = kb * Cfg::kBlockK;
-            if constexpr (kCtas == 2) {
-              tma_load_2d_pair_hint(a_dst, &map_a, kx, g * p.m + a_row, bar, a_policy);
-              tma_load_2d_pair(b_dst, w_map, g * p.k + kx, w_row, bar);
-            } else {
-              tma_load_2d_hint(a_dst, &map_a, kx, g * p.m + a_row, bar, a_policy);
-              tma_load_2d(b_dst, w_map, g * p.k + kx, w_row, bar);
-            }
-          }
-          __syncwarp();
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
-        }
-      }
-    }
-    pdl_launch_dependents();       // all of this CTA's loads are issued: the next kernel may set up
-    if (!ok) __nanosleep(200000);  // let loads already in flight land before teardown
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (rank == 0) {
+  if (warp < Cfg::kFirstEpiWarp) {
+    // grouped form: the first warpgroup (loads, MMAs, two idle warps) gives registers up for the epilogue's
+    if constexpr (kMode == kModeGrouped) setmaxnreg_dec<Cfg::kRegsFrontWarps>();
+    if (warp == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      // The producer and MMA loops are run by their whole warp with one elected lane issuing: the
+      // loop state then lives in uniform registers, which is where TMA and MMA instructions take
+      // their operands. Issued from a single thread inside a divergent branch, every instruction
+      // pays tens of cycles of register moves (measured: 47-76 cycles per MMA against 128 cycles
+      // of tensor-pipe time for a 128 x 256 x 32 step, before the waits and commits).
       int stage = 0;
-      uint32_t phase = 0, acc_iter = 0;
+      uint32_t phase = 0;
+      const uint32_t leader_full0 = kCtas == 2 ? map_to_cta(full_bar(0), 0) : full_bar(0);
+      // the raster keeps a group of A rows in L2 while the weights stream past: A lines leave L2 last
+      const uint64_t a_policy = l2_policy_evict_last();
       bool ok = true;
-      for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
+      bool drew = false;
+      for (int tile = first_tile; ok; tile += tile_stride) {
+        if (tile >= total_tiles) {
+          if (drew || (tile = fetch_piece()) < 0) break;
+          drew = true;
+        }
         int mt, nt, n_start, n_width, g_begin = 0, g_end = p.groups, leftover = -1, tile_index = tile;
         bool alt;
         if constexpr (kMode == kModeGrouped) grouped_item(p, tile, tile_index, g_begin, g_end, leftover);
         tile_coords(p, tile_index, mt, nt, n_start, n_width, alt);
-        // accumulator columns the MMA produces (the biased form adds its 16 ones columns)
-        const uint32_t idesc = idesc_i8(Cfg::kBlockM * kCtas, kMode == kModeBiased ? Cfg::kTileN : n_width,
-                                        /*b_unsigned=*/kMode == kModeBiased);
-        for (int g = g_begin; ok && g < g_end; ++g, ++acc_iter) {
-          const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
-          if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag))) { ok = false; break; }
-          tcgen05_fence_after();
-          const uint32_t tmem_d = tmem_base + buf * Cfg::kTileN;
+        const int a_row = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM;
+        // a pair's CTAs supply half the weight rows each; slices and wide tiles load through their own box
+        // (biased pair: the first CTA loads 128 channels through map_w, the second 120 through the other map)
+        const int w_row = n_start + rank * (kMode == kModeBiased ? Cfg::kBRowsSmem : n_width / kCtas);
+        const CUtensorMap* w_map = (alt || (kMode == kModeBiased && rank == 1)) ? &map_w_slice : &map_w;
+        const uint32_t tx = kMode == kModeBiased
+                                ? static_cast<uint32_t>(kCtas * Cfg::kABytes + Cfg::kChannelsPerTile * Cfg::kBlockK)
+                                : static_cast<uint32_t>(alt ? p.stage_tx_slice : p.stage_tx) * kCtas;
+        for (int g = g_begin; ok && g < g_end; ++g) {
           for (int kb = 0; kb < num_kb; ++kb) {
-            if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(full_bar(stage), phase, abort_flag))) { ok = false; break; }
-            tcgen05_fence_after();
-            const uint32_t a_addr = smem_base + stage * Cfg::kStageBytes;
-            const uint64_t a_desc = smem_desc_sw128(a_addr);
-            const uint64_t b_desc = smem_desc_sw128(a_addr + Cfg::kABytes);
+            if (!__all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag))) { ok = false; break; }
             if (elect_one()) {
-#pragma unroll
-              for (int ks = 0; ks < Cfg::kBlockK / 32; ++ks)
-                mma_i8<kCtas>(tmem_d, a_desc + 2u * ks, b_desc + 2u * ks, idesc,
-                              (kb | ks) != 0 ? 1u : 0u);
+              if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), tx);
+              const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
+              const uint32_t b_dst = a_dst + Cfg::kABytes;
+              const uint32_t bar = leader_full0 + 8u * stage;
+              const int kx = kb * Cfg::kBlockK;
               if constexpr (kCtas == 2) {
-                mma_commit_pair(map_to_cta(empty_bar(stage), 0));
-                mma_commit_pair(map_to_cta(empty_bar(stage), 1));
+                tma_load_2d_pair_hint(a_dst, &map_a, kx, g * p.m + a_row, bar, a_policy);
+                tma_load_2d_pair(b_dst, w_map, g * p.k + kx, w_row, bar);
               } else {
-                mma_commit(empty_bar(stage));
+                tma_load_2d_hint(a_dst, &map_a, kx, g * p.m + a_row, bar, a_policy);
+                tma_load_2d(b_dst, w_map, g * p.k + kx, w_row, bar);
               }
             }
             __syncwarp();
             if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
           }
-          if (!ok) break;
-          if (elect_one()) {
-            if constexpr (kCtas == 2) {
-              mma_commit_pair(map_to_cta(tmem_full_bar(buf), 0));
-              mma_commit_pair(map_to_cta(tmem_full_bar(buf), 1));
-            } else {
-              mma_commit(tmem_full_bar(buf));
-            }
+        }
+      }
+      pdl_launch_dependents();       // all of this CTA's loads are issued: the next kernel may set up
+      if (!ok) __nanosleep(200000);  // let loads already in flight land before teardown
+    } else if (warp == 1) {
+      // ------------------------------------------------------------------ MMA issuer
+      if (rank == 0) {
+        int stage = 0;
+        uint32_t phase = 0, acc_iter = 0;
+        bool ok = true;
+        bool drew = false;
+        for (int tile = first_tile; ok; tile += tile_stride) {
+          if (tile >= total_tiles) {
+            if (drew || (tile = fetch_piece()) < 0) break;
+            drew = true;
           }
-          __syncwarp();
+          int mt, nt, n_start, n_width, g_begin = 0, g_end = p.groups, leftover = -1, tile_index = tile;
+          bool alt;
+          if constexpr (kMode == kModeGrouped) grouped_item(p, tile, tile_index, g_begin, g_end, leftover);
+          tile_coords(p, tile_index, mt, nt, n_start, n_width, alt);
+          // accumulator columns the MMA produces (the biased form adds its 16 ones columns)
+          const uint32_t idesc = idesc_i8(Cfg::kBlockM * kCtas, kMode == kModeBiased ? Cfg::kTileN : n_width,
+                                          /*b_unsigned=*/kMode == kModeBiased);
+          for (int g = g_begin; ok && g < g_end; ++g, ++acc_iter) {
+            const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
+            if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag))) {
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after();
+            const uint32_t tmem_d = tmem_base + buf * Cfg::kTileN;
+            for (int kb = 0; kb < num_kb; ++kb) {
+              if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(full_bar(stage), phase, abort_flag))) {
+                ok = false;
+                break;
+              }
+              tcgen05_fence_after();
+              const uint32_t a_addr = smem_base + stage * Cfg::kStageBytes;
+              const uint64_t a_desc = smem_desc_sw128(a_addr);
+              const uint64_t b_desc = smem_desc_sw128(a_addr + Cfg::kABytes);
+              if (elect_one()) {
+  #pragma unroll
+                for (int ks = 0; ks < Cfg::kBlockK / 32; ++ks)
+                  mma_i8<kCtas>(tmem_d, a_desc + 2u * ks, b_desc + 2u * ks, idesc,
+                                (kb | ks) != 0 ? 1u : 0u);
+                if constexpr (kCtas == 2) {
+                  mma_commit_pair(map_to_cta(empty_bar(stage), 0));
+                  mma_commit_pair(map_to_cta(empty_bar(stage), 1));
+                } else {
+                  mma_commit(empty_bar(stage));
+                }
+              }
+              __syncwarp();
+              if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+            }
+            if (!ok) break;
+            if (elect_one()) {
+              if constexpr (kCtas == 2) {
+                mma_commit_pair(map_to_cta(tmem_full_bar(buf), 0));
+                mma_commit_pair(map_to_cta(tmem_full_bar(buf), 1));
+              } else {
+                mma_commit(tmem_full_bar(buf));
+              }
+            }
+            __syncwarp();
+          }
         }
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int epi = warp - 2;
+    if constexpr (kMode == kModeGrouped) setmaxnreg_inc<Cfg::kRegsEpiWarps>();
+    const int epi = warp - Cfg::kFirstEpiWarp;
     const int quarter = warp & 3;                       // TMEM lanes this warp may read
     const int col_base = (epi >> 2) * Cfg::kColsPerEpiWarp;
     constexpr int kChunks = Cfg::kColsPerEpiWarp / 64;  // 64 output columns per staged box
@@ -495,7 +614,13 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     bool ok = true;
     const uint64_t store_policy = l2_policy_evict_first();
     float total[kMode == kModeGrouped ? Cfg::kColsPerEpiWarp : 1];
-    for (int tile = first_tile; ok && tile < total_tiles; tile += tile_stride) {
+    int piece_tile = -1, piece_group = 0, piece_mt = 0, piece_n0 = 0, piece_width = 0;
+    bool drew = false;
+    for (int tile = first_tile; ok; tile += tile_stride) {
+      if (tile >= total_tiles) {
+        if (drew || (tile = fetch_piece()) < 0) break;
+        drew = true;
+      }
       int mt, nt, n0, n_width;                            // n0 = first output column of this item
       int g_begin = 0, g_end = p.groups, leftover = -1, tile_index = tile;
       bool alt;
@@ -504,18 +629,18 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       const int row0 = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM + quarter * 32;
       const int row = row0 + lane;
       if constexpr (kMode == kModeGrouped) {
-        // the running sums of the previous item are dead (its first group overwrites them): say so, or
-        // they would count as live through the piece code below and push other values out of registers
+        // the running sums of the previous item are dead (this item's first group overwrites them): say so
 #pragma unroll
         for (int t = 0; t < Cfg::kColsPerEpiWarp; ++t) asm volatile("" : "=f"(total[t]));
       }
       for (int g = g_begin; g < g_end; ++g, ++acc_iter) {
         const uint32_t buf = acc_iter & 1u, acc_phase = (acc_iter >> 1) & 1u;
+        // (fetched ahead of the wait: the scale does not depend on the accumulators)
+        const float row_scale = row < p.m ? p.sa[static_cast<size_t>(g) * p.m + row] : 0.f;
         if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(tmem_full_bar(buf), acc_phase, abort_flag))) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                buf * Cfg::kTileN + col_base;
-        const float row_scale = row < p.m ? p.sa[static_cast<size_t>(g) * p.m + row] : 0.f;
         int32_t bias = 0;
         if constexpr (kMode == kModeBiased) {
           uint32_t ones[8];
@@ -614,14 +739,17 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
                 total[t] = g == g_begin ? term : __fadd_rn(total[t], term);
               }
               if (leftover >= 0 && tile_col + half * 32 < n_width) {
-                // a piece: this group's terms of the thread's row, 32 columns, to the workspace
-                const int tile_row = static_cast<int>(rank) * Cfg::kBlockM + quarter * 32 + lane;
-                float* dst = p.terms + ((static_cast<size_t>(leftover) * p.groups + g) * (Cfg::kBlockM * kCtas) + tile_row) * Cfg::kTileN +
-                             tile_col + half * 32;
+                // a piece: this group's terms of the warp's 32 rows x 32 columns to the workspace, in the
+                // order piece_term_index gives (the lanes of a store are adjacent: 512 contiguous bytes)
+                float4* plane = reinterpret_cast<float4*>(p.terms) +
+                                (static_cast<size_t>(leftover) * p.groups + g) * (Cfg::kBlockM * kCtas * Cfg::kTileN / 4);
+                const int row_block = static_cast<int>(rank) * (Cfg::kBlockM / 32) + quarter;
+                const int col_block = (tile_col + half * 32) >> 5;
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
                   const int t = chunk * 64 + half * 32 + j;
-                  __stcg(reinterpret_cast<float4*>(dst + j), make_float4(total[t], total[t + 1], total[t + 2], total[t + 3]));
+                  __stcg(plane + piece_term_index(row_block, col_block, j >> 2, lane),
+                         make_float4(total[t], total[t + 1], total[t + 2], total[t + 3]));
                 }
               }
             }
@@ -737,12 +865,21 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
       if constexpr (kMode == kModeGrouped) {
-        if (leftover >= 0) {
-          // ---- a piece: wait for the other pieces of this tile, then finish this piece's share of it
-          finish_piece<kCtas, kMode>(p.terms, p.piece_sync, p.sw, p.out, p.m, p.n, p.groups, leftover, g_begin, mt, n0, n_width,
-                                     static_cast<int>(rank), epi, lane, out_vec, abort_flag);
+        if (leftover >= 0) {   // a piece is always a worker's last item: remember it and finish it below
+          piece_tile = leftover;
+          piece_group = g_begin;
+          piece_mt = mt;
+          piece_n0 = n0;
+          piece_width = n_width;
         }
       }
+    }
+    if constexpr (kMode == kModeGrouped) {
+      // ---- a piece: wait for the other pieces of its tile, then finish this piece's share of it. Done behind
+      // the item loop, where the running sums are dead and their registers free for the terms in flight.
+      if (piece_tile >= 0 && ok)
+        finish_piece<kCtas, kMode>(p.terms, p.piece_sync, p.sw, p.out, p.m, p.n, p.groups, piece_tile, piece_group, piece_mt,
+                                   piece_n0, piece_width, static_cast<int>(rank), epi, lane, out_vec, abort_flag);
     }
     if ((tma_out || ws_tma) && lane == 0) {
       // staged boxes must outlive their stores; before the rendezvous the stores must have landed as well

@@ -236,6 +236,18 @@ __device__ __forceinline__ void st_relaxed_u64(unsigned long long* address, unsi
 }
 
 // ---------------------------------------------------------------- cluster
+// Register reallocation between the warpgroups of a CTA (all four warps of a warpgroup execute it together):
+// dec returns this warpgroup's registers above `kRegs` per thread to the CTA's pool, inc waits until the
+// pool can raise this warpgroup to `kRegs` per thread. kRegs: a multiple of 8 in 24..256.
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -251,6 +263,10 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta)
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
   return r;
+}
+// 32-bit store into another CTA's shared memory (address from map_to_cta)
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t value) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(value) : "memory");
 }
 
 // ---------------------------------------------------------------- tcgen05 / TMEM

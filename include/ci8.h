@@ -98,7 +98,8 @@ int ci8_grouped_channel_mm(const int8_t* codes, const int8_t* w, const float* sc
 /* ci8_grouped_channel_mm with a caller-lent workspace (no counterpart in the reference). When the tiles
  * of the last wave would leave most of the GPU idle (M = 2048, N = 7168 on 148 SMs: 224 tiles of 256 x 256
  * for 74 CTA pairs, so two tiles in a fourth wave), those tiles are cut along the groups: every group of
- * such a tile runs on a CTA pair of its own, writes its FP32 terms to the workspace, and the pairs then
+ * such a tile runs on a CTA pair of its own (the pairs that finish their whole tiles first draw the
+ * pieces from a counter in the workspace), writes its FP32 terms to the workspace, and the pairs then
  * add the terms in ascending group order, the same fadd chain as without the split, so the output
  * has the same bits. ci8_grouped_workspace_bytes() tells how much the shape needs on the current device
  * (0: the split would not pay and no workspace is used). The workspace must be 16-byte aligned and
