@@ -717,15 +717,12 @@ __global__ void peer_rendezvous_kernel(const RendezvousParams p) {
 }  // namespace
 
 // ------------------------------------------------------------------ block-32 (Q8_0) launch
-cudaError_t launch_q8_block(const void* x, int8_t* a, float* sa, const int8_t* w, const void* sw, void* y, int m,
-                            int n, int k, cudaStream_t stream) {
-  using Cfg = Q8BlockConfig;
+template <int kTileN>
+cudaError_t launch_q8_block_mm(const int8_t* a, const float* sa, const int8_t* w, const void* sw, void* y, int m, int n,
+                               int k, cudaStream_t stream) {
+  using Cfg = Q8BlockConfig<kTileN>;
   static std::atomic<uint64_t> smem_done{0};
-  cudaError_t err = ensure_smem(q8_block_mm_kernel, Cfg::kSmemBytes, smem_done);
-  if (err != cudaSuccess) return err;
-  const long long blocks = static_cast<long long>(m) * (k / 32);
-  err = launch_serialized(q8_block_quantize_kernel, static_cast<unsigned>((blocks + 255) / 256), 256, 0, stream,
-                          static_cast<const uint16_t*>(x), a, sa, static_cast<int64_t>(blocks));
+  cudaError_t err = ensure_smem(q8_block_mm_kernel<kTileN>, Cfg::kSmemBytes, smem_done);
   if (err != cudaSuccess) return err;
   Q8BlockParams p{sa, static_cast<const __half*>(sw), static_cast<__nv_bfloat16*>(y), m, n, k, 0, 0};
   p.tiles_m = (m + Cfg::kBlockM - 1) / Cfg::kBlockM;
@@ -737,8 +734,39 @@ cudaError_t launch_q8_block(const void* x, int8_t* a, float* sa, const int8_t* w
   if (err != cudaSuccess) return err;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   const int sms = sm_count();
-  return launch_serialized(q8_block_mm_kernel, static_cast<unsigned>(tiles < sms ? tiles : sms), Cfg::kThreads,
+  return launch_serialized(q8_block_mm_kernel<kTileN>, static_cast<unsigned>(tiles < sms ? tiles : sms), Cfg::kThreads,
                            Cfg::kSmemBytes, stream, map_a, map_w, p);
+}
+
+// Channels per tile of the block-32 kernel: a tile's time is its epilogue's (the FP32 rescale of every 32-deep
+// partial sum), and the persistent grid runs the tiles in waves of one per SM. Measured on M=4096, N=1024,
+// K=4096: four waves of 64-wide tiles 121 us, seven waves of 32-wide ones 135 us, so a wave of width w costs about
+// w + 24 (per stage the barrier round trips, the scale hand-over and the accumulator loads do not shrink with
+// the width). Narrow tiles pay where the wide one leaves SMs without work: M=16, N=1024 32.0 -> 19.4 us with
+// 16-wide tiles on 64 SMs instead of 64-wide ones on 16. Ties go to the wider tile, which loads A less often.
+int q8_block_tile_channels(int m, int n) {
+  const long long tiles_m = (m + 127) / 128, sms = sm_count();
+  int best = 64;
+  long long best_cost = 0;
+  for (int width = 64; width >= 16; width /= 2) {
+    const long long tiles = tiles_m * ((n + width - 1) / width);
+    const long long cost = ((tiles + sms - 1) / sms) * (width + 24);
+    if (width == 64 || cost * 100 < best_cost * 97) { best = width; best_cost = cost; }
+  }
+  return best;
+}
+
+cudaError_t launch_q8_block(const void* x, int8_t* a, float* sa, const int8_t* w, const void* sw, void* y, int m,
+                            int n, int k, cudaStream_t stream) {
+  const long long blocks = static_cast<long long>(m) * (k / 32);
+  cudaError_t err = launch_serialized(q8_block_quantize_kernel, static_cast<unsigned>((blocks + 255) / 256), 256, 0, stream,
+                                      static_cast<const uint16_t*>(x), a, sa, static_cast<int64_t>(blocks));
+  if (err != cudaSuccess) return err;
+  switch (q8_block_tile_channels(m, n)) {
+    case 16: return launch_q8_block_mm<16>(a, sa, w, sw, y, m, n, k, stream);
+    case 32: return launch_q8_block_mm<32>(a, sa, w, sw, y, m, n, k, stream);
+    default: return launch_q8_block_mm<64>(a, sa, w, sw, y, m, n, k, stream);
+  }
 }
 
 // ------------------------------------------------------------------ block-32 with built-in scratch
@@ -1121,6 +1149,8 @@ int ci8_q8_block_mm_static(const void* x, const int8_t* w, const void* sw, void*
 }
 
 int ci8_q8_block_static_max_values(void) { return static_cast<int>(kQ8StaticMaxValues); }
+
+int ci8_q8_block_tile_channels(int m, int n) { return (m > 0 && n > 0) ? q8_block_tile_channels(m, n) : 0; }
 
 int ci8_gemm_tile_plan(int m, int n, int k, int groups, int* plan) {
   if (!plan || m <= 0 || n <= 0 || k <= 0 || groups <= 0) return kInvalid;

@@ -69,28 +69,35 @@ struct Q8BlockParams {
   int tiles_m, tiles_n;
 };
 
+// kTileNT: output channels per tile, 64, 32 or 16. The time of a tile is its epilogue's, which is proportional
+// to the channels; the host takes a narrower tile when the wider one would leave the last wave (or, for a small
+// problem, most of the SMs) without work.
+template <int kTileNT>
 struct Q8BlockConfig {
+  static_assert(kTileNT == 64 || kTileNT == 32 || kTileNT == 16, "tile widths: 64, 32 or 16 channels");
   static constexpr int kBlockM = 128;                  // rows of A per tile
-  static constexpr int kTileN = 64;                    // output channels per tile
+  static constexpr int kTileN = kTileNT;               // output channels per tile
   static constexpr int kBlockK = 128;                  // bytes of K per stage = four 32-wide blocks
   static constexpr int kBlocksPerStage = kBlockK / 32;
   static constexpr int kABytes = kBlockM * kBlockK;
   static constexpr int kWBytes = kTileN * kBlockK;
   static constexpr int kStageBytes = kABytes + kWBytes;
   static constexpr int kStages = 6;
-  static constexpr int kEpiWarps = 8;                  // two per TMEM lane quarter, 32 channels each
+  static constexpr int kEpiWarps = 8;                  // two per TMEM lane quarter, half of the tile's channels each
+  static constexpr int kWarpColumns = kTileN / 2;      // channels per epilogue warp
   static constexpr int kThreads = (2 + kEpiWarps) * 32;
-  static constexpr int kAccColumns = kBlocksPerStage * kTileN;   // 256: one half of TMEM per stage
+  static constexpr int kAccColumns = kBlocksPerStage * kTileN;   // at most 256: one half of TMEM per stage
   static constexpr int kScaleBytes = kEpiWarps * kBlocksPerStage * 32 * 4;   // FP32 weight scales per warp
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = kStages * kStageBytes + kScaleBytes + kBarrierBytes + 1024;
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
-__global__ void __launch_bounds__(Q8BlockConfig::kThreads, 1)
+template <int kTileN>
+__global__ void __launch_bounds__(Q8BlockConfig<kTileN>::kThreads, 1)
 q8_block_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                    const Q8BlockParams p) {
-  using Cfg = Q8BlockConfig;
+  using Cfg = Q8BlockConfig<kTileN>;
   extern __shared__ uint8_t q8_smem_raw[];
   const uint32_t raw_addr = smem_u32(q8_smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -190,18 +197,20 @@ q8_block_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     // ------------------------------------------------------------------ epilogue: rescale and add
     const int epi = warp - 2;
     const int quarter = warp & 3;                 // TMEM lanes this warp may read
-    const int half = epi >> 2;                    // which 32 of the tile's 64 channels
+    const int half = epi >> 2;                    // which half of the tile's channels
+    constexpr int kCols = Cfg::kWarpColumns;
     float* my_scales = scale_region + epi * (Cfg::kBlocksPerStage * 32);   // [block][channel]
     uint32_t iter = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
       const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
       const int row = mt * Cfg::kBlockM + quarter * 32 + lane;
-      const int col0 = nt * Cfg::kTileN + half * 32;          // first channel of this warp
+      const int col0 = nt * Cfg::kTileN + half * kCols;       // first channel of this warp
       const int my_col = col0 + lane;                         // the channel whose scales this lane fetches
-      float2 sum2[16];                                        // sums of channels 2i and 2i + 1
+      const bool my_col_live = lane < kCols && my_col < p.n;  // (lanes past the warp's channels fetch nothing)
+      float2 sum2[kCols / 2];                                 // sums of channels 2i and 2i + 1
 #pragma unroll
-      for (int c = 0; c < 16; ++c) sum2[c] = make_float2(0.f, 0.f);
+      for (int c = 0; c < kCols / 2; ++c) sum2[c] = make_float2(0.f, 0.f);
       // Scales of a stage's four blocks (zero past the end of K, of M or of N). Those of the next
       // stage are fetched while the current one is processed, and kept as the raw loaded words: any
       // arithmetic on them here would wait for the loads.
@@ -219,7 +228,7 @@ q8_block_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (vector_scales) {
           // the stage's four blocks are adjacent: one 16-byte and one 8-byte load per thread
           if (row < p.m) next_row_scales = __ldg(reinterpret_cast<const float4*>(sa_row));
-          if (my_col < p.n) next_channel_scales = __ldg(reinterpret_cast<const uint2*>(sw_row));
+          if (my_col_live) next_channel_scales = __ldg(reinterpret_cast<const uint2*>(sw_row));
         } else {
           const int live = min(Cfg::kBlocksPerStage, blocks_in_row - first);
           if (row < p.m) {
@@ -228,7 +237,7 @@ q8_block_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             if (live > 2) next_row_scales.z = __ldg(sa_row + 2);
             if (live > 3) next_row_scales.w = __ldg(sa_row + 3);
           }
-          if (my_col < p.n) {
+          if (my_col_live) {
             uint32_t h0 = __ldg(sw_row), h1 = 0u, h2 = 0u, h3 = 0u;
             if (live > 1) h1 = __ldg(sw_row + 1);
             if (live > 2) h2 = __ldg(sw_row + 2);
@@ -254,20 +263,20 @@ q8_block_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         fetch_scales(kb + 1);   // past the last stage every block index is out of range: zeros, no loads
         if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), buf_phase, abort_flag))) { ok = false; break; }
         tcgen05_fence_after();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * Cfg::kAccColumns + half * 32;
-        uint32_t v[2][32];
-        tmem_ld_32x32(taddr, v[0]);
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * Cfg::kAccColumns + half * kCols;
+        uint32_t v[2][kCols];
+        tmem_ld_columns(taddr, v[0]);
 #pragma unroll
         for (int b = 0; b < Cfg::kBlocksPerStage; ++b) {
-          uint32_t (&cur)[32] = v[b & 1];
+          uint32_t (&cur)[kCols] = v[b & 1];
           tmem_ld_wait_for(cur);
-          if (b + 1 < Cfg::kBlocksPerStage) tmem_ld_32x32(taddr + (b + 1) * Cfg::kTileN, v[(b + 1) & 1]);
+          if (b + 1 < Cfg::kBlocksPerStage) tmem_ld_columns(taddr + (b + 1) * Cfg::kTileN, v[(b + 1) & 1]);
           const float4* channel_scales = reinterpret_cast<const float4*>(my_scales + b * 32);   // broadcast reads
           // packed FP32 arithmetic (two IEEE-rounded lanes per instruction): one multiply for two scale
           // products, one FMA for two accumulations
           const float2 rs2 = make_float2(row_scale[b], row_scale[b]);
 #pragma unroll
-          for (int c = 0; c < 32; c += 4) {
+          for (int c = 0; c < kCols; c += 4) {
             const float4 s = channel_scales[c >> 2];
             const float2 f01 = make_float2(__int2float_rn(static_cast<int32_t>(cur[c])), __int2float_rn(static_cast<int32_t>(cur[c + 1])));
             const float2 f23 = make_float2(__int2float_rn(static_cast<int32_t>(cur[c + 2])), __int2float_rn(static_cast<int32_t>(cur[c + 3])));
@@ -284,15 +293,15 @@ q8_block_mm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       if (row < p.m) {
         __nv_bfloat16* dst = p.y + static_cast<size_t>(row) * p.n + col0;
         const int limit = p.n - col0;
-        if (limit >= 32 && p.n % 8 == 0 && reinterpret_cast<uintptr_t>(p.y) % 16 == 0) {
+        if (limit >= kCols && p.n % 8 == 0 && reinterpret_cast<uintptr_t>(p.y) % 16 == 0) {
 #pragma unroll
-          for (int c = 0; c < 16; c += 4)
+          for (int c = 0; c < kCols / 2; c += 4)
             *reinterpret_cast<uint4*>(dst + 2 * c) =
                 make_uint4(pack_bf16x2(sum2[c].x, sum2[c].y), pack_bf16x2(sum2[c + 1].x, sum2[c + 1].y),
                            pack_bf16x2(sum2[c + 2].x, sum2[c + 2].y), pack_bf16x2(sum2[c + 3].x, sum2[c + 3].y));
         } else {
 #pragma unroll
-          for (int c = 0; c < 32; ++c)
+          for (int c = 0; c < kCols; ++c)
             if (c < limit) dst[c] = __float2bfloat16_rn((c & 1) ? sum2[c >> 1].y : sum2[c >> 1].x);
         }
       }

@@ -394,8 +394,25 @@ __device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&v)[32]) {
                :
                : "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&v)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+               :
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&v)[8]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7])
+               :
+               : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// 32 lanes x (array length) columns, chosen by the destination's size
+__device__ __forceinline__ void tmem_ld_columns(uint32_t taddr, uint32_t (&v)[32]) { tmem_ld_32x32(taddr, v); }
+__device__ __forceinline__ void tmem_ld_columns(uint32_t taddr, uint32_t (&v)[16]) { tmem_ld_32x16(taddr, v); }
+__device__ __forceinline__ void tmem_ld_columns(uint32_t taddr, uint32_t (&v)[8]) { tmem_ld_32x8(taddr, v); }
 
 }  // namespace ci8

@@ -228,6 +228,11 @@ int ci8_decode_mm_split(const int8_t* a, const void* w, const float* a_scale, co
  * the tiles of the last wave are cut into. Tests use it to make sure every form is exercised. */
 int ci8_gemm_tile_plan(int m, int n, int k, int groups, int* plan);
 
+/* Diagnostic (no counterpart in the reference): output channels per tile (64, 32 or 16) the block-32
+ * kernel takes for an [m, n] result on the current device, or 0 for a bad argument. Tests use it to make
+ * sure every width is exercised. */
+int ci8_q8_block_tile_channels(int m, int n);
+
 /* Self-test of the kernels' bounded waits (no counterpart in the reference): launches one CTA that
  * waits on a barrier nothing arrives on; after deadline_us microseconds (1..1000000) the wait
  * gives up exactly as the production kernels' waits do after their 2 s deadline: status bit 0 is

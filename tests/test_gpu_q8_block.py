@@ -33,8 +33,18 @@ def _call(ops, x, a, sa, w, sw, y, m, n, k):
     return ops.libci8.ci8_q8_block_mm(_ptr(x), _ptr(a), _ptr(sa), _ptr(w), _ptr(sw), _ptr(y), m, n, k, stream)
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 1, 32), (17, 33, 96), (129, 65, 256), (16, 200, 4096), (300, 130, 1056),
-                                   (1024, 1024, 1024)])
+CASES = [(1, 1, 32), (17, 33, 96), (129, 65, 256), (16, 200, 4096), (300, 130, 1056), (1024, 1024, 1024),
+         (384, 800, 128), (384, 812, 64)]
+
+
+def test_cases_cover_every_tile_width(ops):
+    """The kernel comes in tiles of 64, 32 and 16 channels, chosen from the shape and the SM count."""
+    widths = {ops.libci8.ci8_q8_block_tile_channels(m, n) for m, n, _ in CASES}
+    assert widths == {16, 32, 64}, widths
+    assert ops.libci8.ci8_q8_block_tile_channels(0, 4) == 0
+
+
+@pytest.mark.parametrize("m,n,k", CASES)
 def test_block32_matches_checker_bit_for_bit(ops, m, n, k):
     x, w, sw = _case(m, n, k, 7 * m + n)
     dx, dw, dsw = x.to(DEV), w.to(DEV), sw.to(DEV)
