@@ -161,8 +161,25 @@ decode_w8a8_kernel(const __grid_constant__ CUtensorMap map_w,
   // warps) or in the teardown (everybody else), so nobody blocks here.
   if constexpr (kSplit > 1) cluster_arrive();
   const uint32_t tmem_base = *tmem_slot;
-  // Everything above touched only shared memory, TMEM and kernel parameters; from here on global
-  // memory is read and written, so the previous kernel in the stream must have finished.
+  // Everything above touched only shared memory, TMEM and kernel parameters. While the previous kernel in
+  // the stream drains (this CTA got its SM when one of that kernel's CTAs left; the whole grid may take a few
+  // more microseconds to finish and flush), the weight tiles of the first ring-full of stages are prefetched
+  // into L2, in the producer's order: HBM would otherwise sit idle across the kernel boundary, and the first
+  // loads after the wait would each pay a DRAM round trip. A prefetch reads nothing into the SM (see
+  // tma_prefetch_l2_2d), so it needs no ordering against the previous kernel.
+  if (warp == Cfg::kTmaWarp && kb_end > kb_begin) {
+    if (elect_one()) {
+      const int count = kb_end - kb_begin;
+      const int ahead = count < num_stages ? count : num_stages;
+      int kb = kb_begin + (slab_index * 5) % count;
+      for (int i = 0; i < ahead; ++i) {
+        tma_prefetch_l2_2d(&map_w, kb * Cfg::kBlockK, n0);
+        if (++kb == kb_end) kb = kb_begin;
+      }
+    }
+    __syncwarp();
+  }
+  // From here on global memory is read and written, so the previous kernel in the stream must have finished.
   pdl_launch_dependents();
   pdl_wait();
 

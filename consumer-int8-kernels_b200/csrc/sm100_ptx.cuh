@@ -127,6 +127,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void prefetch_tensormap(const void* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
+// 2-D tile prefetch into L2: nothing is read into the SM and no barrier is involved. L2 is where all SMs'
+// writes meet, so a prefetch can run ahead of griddepcontrol.wait even for data the previous kernel is still
+// writing: the real load, issued after the wait, sees whatever the line holds by then.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y)
+               : "memory");
+}
 // 2-D tile load, global -> this CTA's shared memory, completion on this CTA's mbarrier.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* map, int x, int y,
                                             uint32_t bar) {
