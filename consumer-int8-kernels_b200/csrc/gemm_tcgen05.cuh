@@ -628,6 +628,16 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       tile_coords(p, tile_index, mt, nt, n0, n_width, alt);
       const int row0 = mt * (Cfg::kBlockM * kCtas) + rank * Cfg::kBlockM + quarter * 32;
       const int row = row0 + lane;
+      // Channel scales of this warp's columns, all fetched here, ahead of the accumulators: lane j of word i
+      // holds sw[n0 + col_base + 32 i + j]. Fetched where each 32-column half needs them, every half began with
+      // a round trip to L2 (cycle stamps: 1100 cycles per half, 10 k for a tile's epilogue; hidden behind the
+      // next tile's MMAs, but not behind the last one's).
+      float tile_sw[Cfg::kColsPerEpiWarp / 32];
+#pragma unroll
+      for (int i = 0; i < Cfg::kColsPerEpiWarp / 32; ++i) {
+        const int channel = n0 + col_base + i * 32 + lane;
+        tile_sw[i] = channel < p.n ? __bfloat162float(p.sw[channel]) : 0.f;
+      }
       if constexpr (kMode == kModeGrouped) {
         // the running sums of the previous item are dead (this item's first group overwrites them): say so
 #pragma unroll
@@ -672,9 +682,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
               tmem_ld_wait_for(vu);
               if (!store_box) continue;
               // channel scales: lane j holds those of gate column j and up column j of this half box
-              const int gate_n = n0 + gate_col + lane, up_n = gate_n + Cfg::kTileN / 2;
-              const float my_gate_sw = gate_n < p.n ? __bfloat162float(p.sw[gate_n]) : 0.f;
-              const float my_up_sw = up_n < p.n ? __bfloat162float(p.sw[up_n]) : 0.f;
+              const float my_gate_sw = tile_sw[boxi * 2 + half], my_up_sw = tile_sw[Cfg::kTileN / 64 + boxi * 2 + half];
               uint32_t packed[16];
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
@@ -755,7 +763,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
             }
             if (!store_box || h0 >= p.n || tile_col + half * 32 >= n_width) continue;
             // channel scales of these 32 columns: lane j holds sw[h0 + j]
-            const float my_sw = (h0 + lane < p.n) ? __bfloat162float(p.sw[h0 + lane]) : 0.f;
+            const float my_sw = tile_sw[chunk * 2 + half];
             const int limit = kMode == kModeBiased
                                   ? min(p.n - h0, n_width - (tile_col + half * 32))
                                   : p.n - h0;
