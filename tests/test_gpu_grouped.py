@@ -74,6 +74,27 @@ def test_grouped_split_along_the_groups_matches_checker(ops, m, n, groups):
     assert device_status(ops) == 0
 
 
+def test_grouped_split_takes_channel_scales_at_any_alignment(ops):
+    """The pieces read their channel scales eight at a time when the pointer allows it and one by one
+    when it does not: a scale vector that starts two bytes into an allocation gives the same bits."""
+    m, n, groups = 520, 700, 4
+    need = ops.grouped_workspace_bytes(m, n, groups)
+    assert need > 0
+    inputs = workloads.grouped_inputs(m, n, groups, seed=77)
+    codes, scales = ref.quantize_grouped4096_ref(inputs.x)
+    want = ref.grouped_channel_mm_ref(codes, scales, inputs.w, inputs.w_scale, fast=True)
+    holder = torch.empty(n + 1, dtype=torch.bfloat16, device=DEV)
+    holder[1:].copy_(inputs.w_scale)
+    shifted = holder[1:]
+    assert shifted.data_ptr() % 16 != 0
+    workspace = torch.zeros(need, dtype=torch.uint8, device=DEV)
+    out, check = guarded((m, n), torch.bfloat16, float("nan"))
+    ops.grouped_channel_mm_ws(codes.to(DEV), inputs.w.to(DEV), scales.to(DEV), shifted, workspace, out)
+    assert_bit_equal(out, want, "split along the groups, unaligned channel scales")
+    check()
+    assert device_status(ops) == 0
+
+
 def test_grouped_split_replays_from_a_graph(ops):
     m, n, groups = 520, 700, 4
     need = ops.grouped_workspace_bytes(m, n, groups)
