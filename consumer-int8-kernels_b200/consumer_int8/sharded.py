@@ -148,7 +148,7 @@ class ColumnShardedLinear:
                     gathered=flat.view(plan.gathered_shape),
                     peer_ptrs=torch.tensor([int(p) for p in handle.buffer_ptrs], dtype=torch.int64),
                     signal_ptrs=torch.tensor([int(p) for p in counter_handle.buffer_ptrs], dtype=torch.int64),
-                    state=torch.zeros(2, dtype=torch.int64, device=device),
+                    state=torch.zeros(4, dtype=torch.int64, device=device),   # calls done, CTAs gone, tiles drawn, spare
                     keep=(handle, counter_handle, counters),     # keeps the peer mappings alive
                 ))
             torch.cuda.synchronize(device)

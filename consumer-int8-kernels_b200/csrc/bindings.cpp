@@ -317,7 +317,7 @@ void boxed_gate_up_silu_mm(StableIValue* stack, uint64_t, uint64_t) {
 // block `rank` of every rank's gathered buffer [world, M, N/world] (peer-mapped symmetric memory).
 // peer_ptrs is a CPU INT64 tensor holding the device address of every rank's buffer. The _sync form
 // also takes signal_ptrs (CPU INT64, the address of every rank's arrival counters) and state (INT64
-// [2] on this device) and ends with the in-kernel cross-GPU rendezvous.
+// [4] on this device) and ends with the in-kernel cross-GPU rendezvous.
 void gather_common(StableIValue* stack, bool sync) {
   auto a = to<Tensor>(stack[0]), w = to<Tensor>(stack[1]);
   auto sa = to<Tensor>(stack[2]), sw = to<Tensor>(stack[3]);
@@ -358,7 +358,7 @@ void gather_common(StableIValue* stack, bool sync) {
   }
   auto signal_ptrs = to<Tensor>(stack[6]), state = to<Tensor>(stack[7]);
   check(state, ScalarType::Long, device);
-  STD_TORCH_CHECK(state.numel() == 2, "state must hold two INT64 words");
+  STD_TORCH_CHECK(state.numel() == 4, "state must hold four INT64 words");
   STD_TORCH_CHECK(!signal_ptrs.is_cuda() && signal_ptrs.is_contiguous() && signal_ptrs.scalar_type() == ScalarType::Long &&
                       signal_ptrs.dim() == 1 && signal_ptrs.size(0) == world,
                   "signal_ptrs must be a contiguous CPU INT64 vector with one entry per rank");
@@ -378,7 +378,7 @@ void boxed_peer_rendezvous(StableIValue* stack, uint64_t, uint64_t) {
   const int64_t rank = to<int64_t>(stack[2]);
   const int device = state.get_device_index();
   check(state, ScalarType::Long, device);
-  STD_TORCH_CHECK(state.numel() == 2, "state must hold two INT64 words");
+  STD_TORCH_CHECK(state.numel() == 2 || state.numel() == 4, "state must hold two (or the gathering operator's four) INT64 words");
   STD_TORCH_CHECK(!signal_ptrs.is_cuda() && signal_ptrs.is_contiguous() && signal_ptrs.scalar_type() == ScalarType::Long &&
                       signal_ptrs.dim() == 1 && signal_ptrs.size(0) > 0 && signal_ptrs.size(0) <= 8,
                   "signal_ptrs must be a contiguous CPU INT64 vector with one entry per rank");

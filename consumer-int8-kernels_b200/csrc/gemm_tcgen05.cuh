@@ -84,6 +84,15 @@ struct GemmParams {
 // arrival and departure counters of the leftover tiles (two each, at most 37 tiles on 74 workers).
 constexpr int kPieceFetchWord = 192;
 
+// Gathering form with the in-kernel rendezvous: after its first tile a worker does not walk the tiles with a
+// fixed stride but draws the next one from a counter (state[2]). The CTAs of a GPU do not get equal shares of a
+// saturated NVLink, and their tile stores are what paces them: with a fixed assignment the slowest CTA issued
+// its last store 10 % after the median one. The worker's load warp draws and announces the tile to the other
+// roles (of both CTAs of a pair) through a ring of kDrawSlots shared-memory words with a barrier each; the load
+// warp is never more than the ring's stages plus the two accumulator buffers ahead of the slowest reader, which
+// is less than kDrawSlots tiles.
+constexpr int kDrawSlots = 16;
+
 // Grouped form: item -> the tile index tile_coords takes, the groups [g_begin, g_end) the item covers
 // and, for a piece, the index of its tile among the leftover tiles (-1 for a whole tile).
 __device__ __forceinline__ void grouped_item(const GemmParams& p, int item, int& tile, int& g_begin, int& g_end,
@@ -109,7 +118,8 @@ __device__ __forceinline__ void grouped_item(const GemmParams& p, int item, int&
 // each of its own GPU's counters shows that all CTAs of that rank have arrived for this call: when the
 // kernel ends, the whole gathered result is in this GPU's memory. state (two 64-bit words in this
 // GPU's memory, zero at first) counts the calls, so that a call can be replayed from a CUDA graph:
-// state[0] = completed calls, state[1] = CTAs of the running call that have left.
+// state[0] = completed calls, state[1] = CTAs of the running call that have left, state[2] = tiles drawn in
+// the running call (see kDrawSlots), zero between calls; state[3] is spare.
 struct OutputMaps {
   CUtensorMap map[kMaxOutputs];
   unsigned long long* signal[kMaxOutputs];
@@ -150,7 +160,7 @@ struct GemmConfig {
   static constexpr int kStoreBufs = kEpiWarps == 4 ? 2 : 1;   // staging boxes per epilogue warp
   static constexpr int kWsBufs = kMode == kModeWorkspace ? 2 : 0;   // INT32 staging boxes (32 x 32) per epilogue warp
   static constexpr int kStagingBytes = kEpiWarps * (kStoreBufs + kWsBufs) * kStoreBoxBytes;
-  static constexpr int kBarrierBytes = 256;
+  static constexpr int kBarrierBytes = 512;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
   static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
@@ -378,6 +388,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   // grouped form with pieces: the barrier the piece's number is announced on, and the number
   const uint32_t piece_bar = bar_base + 8u * (2 * Cfg::kStages + 5);
   volatile int* piece_slot = reinterpret_cast<volatile int*>(bar_region + 8 * (2 * Cfg::kStages + 6));
+  // drawn tiles (see kDrawSlots): barriers at byte 192, the tiles' numbers behind them
+  auto draw_bar = [&](int i) { return bar_base + 192u + 8u * i; };
+  volatile int* draw_slot = reinterpret_cast<volatile int*>(bar_region + 192 + 8 * kDrawSlots);
 
   const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);   // provably warp-uniform
   const int lane = threadIdx.x & 31;
@@ -393,6 +406,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(tmem_empty_bar(b), Cfg::kEpiWarps * kCtas);
     }
     if constexpr (kMode == kModeGrouped) mbar_init(piece_bar, 1);
+    if (out_maps.state != nullptr)
+      for (int i = 0; i < kDrawSlots; ++i) mbar_init(draw_bar(i), 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -473,6 +488,32 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
   };
   const int first_tile = kCtas == 2 ? (blockIdx.x >> 1) : blockIdx.x;
   const int tile_stride = kCtas == 2 ? (gridDim.x >> 1) : gridDim.x;
+  // The item after `tile` for the calling warp (all of its lanes): the fixed stride, or in the gathering form
+  // with a rendezvous the worker's next draw (`draws` counts them per role; a value past the last item ends the
+  // walk for every role alike, and an abandoned wait returns one as well).
+  const bool drawn = kMode == kModeFused && out_maps.state != nullptr;
+  auto next_item = [&](int tile, int& draws) -> int {
+    if (!drawn) return tile + tile_stride;
+    const int slot = draws % kDrawSlots;                                          // draw number `draws`, from zero
+    const uint32_t parity = static_cast<uint32_t>(draws / kDrawSlots) & 1u;       // how often the slot was used before
+    ++draws;
+    int value = 0;
+    if (warp == 0 && rank == 0) {
+      if (lane == 0) {
+        value = tile_stride + static_cast<int>(atomicAdd(out_maps.state + 2, 1ull));
+        draw_slot[slot] = value;
+        if constexpr (kCtas == 2)
+          st_shared_cluster_u32(map_to_cta(smem_u32(const_cast<int*>(draw_slot + slot)), 1), static_cast<uint32_t>(value));
+        mbar_arrive(draw_bar(slot));
+        if constexpr (kCtas == 2) mbar_arrive_cluster(draw_bar(slot), 1);
+      }
+      value = __shfl_sync(0xffffffffu, value, 0);
+    } else {
+      if (!__all_sync(0xffffffffu, mbar_wait<kCtas == 2>(draw_bar(slot), parity, abort_flag))) return 0x7fffffff;
+      value = draw_slot[slot];
+    }
+    return value;
+  };
 
   if (warp < Cfg::kFirstEpiWarp) {
     // grouped form: the first warpgroup (loads, MMAs, two idle warps) gives registers up for the epilogue's
@@ -491,7 +532,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint64_t a_policy = l2_policy_evict_last();
       bool ok = true;
       bool drew = false;
-      for (int tile = first_tile; ok; tile += tile_stride) {
+      int draws = 0;
+      for (int tile = first_tile; ok; tile = next_item(tile, draws)) {
         if (tile >= total_tiles) {
           if (drew || (tile = fetch_piece()) < 0) break;
           drew = true;
@@ -539,7 +581,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
         uint32_t phase = 0, acc_iter = 0;
         bool ok = true;
         bool drew = false;
-        for (int tile = first_tile; ok; tile += tile_stride) {
+        int draws = 0;
+        for (int tile = first_tile; ok; tile = next_item(tile, draws)) {
           if (tile >= total_tiles) {
             if (drew || (tile = fetch_piece()) < 0) break;
             drew = true;
@@ -616,7 +659,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     float total[kMode == kModeGrouped ? Cfg::kColsPerEpiWarp : 1];
     int piece_tile = -1, piece_group = 0, piece_mt = 0, piece_n0 = 0, piece_width = 0;
     bool drew = false;
-    for (int tile = first_tile; ok; tile += tile_stride) {
+    int draws = 0;
+    for (int tile = first_tile; ok; tile = next_item(tile, draws)) {
       if (tile >= total_tiles) {
         if (drew || (tile = fetch_piece()) < 0) break;
         drew = true;
@@ -933,6 +977,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_a,
     __threadfence();
     if (atomicAdd(out_maps.state + 1, 1ull) == gridDim.x - 1ull) {
       out_maps.state[1] = 0ull;
+      out_maps.state[2] = 0ull;   // every worker has drawn its last tile: the next call draws from zero again
       __threadfence();
       st_relaxed_u64(out_maps.state, calls_done + 1ull);
     }

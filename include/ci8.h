@@ -189,8 +189,10 @@ int ci8_fused_channel_mm_gather(const int8_t* a, const int8_t* w, const float* a
 /* ci8_fused_channel_mm_gather with the closing cross-GPU barrier inside the kernel (no counterpart in
  * the reference). signals[r] (a HOST array of device pointers, r = 0..world-1) points to 8 arrival
  * counters of 8 bytes each in rank r's memory, peer-mapped into this process like the gathered
- * buffers, zero before the first call and never reset; state points to 16 zero-initialised bytes in
- * THIS rank's memory. Every CTA signals every rank after its stores have landed and then waits until
+ * buffers, zero before the first call and never reset; state points to 32 zero-initialised bytes in
+ * THIS rank's memory (calls completed, CTAs gone, tiles drawn: after its first tile a worker of this
+ * form draws its next tile from a counter, because the CTAs do not get equal shares of a saturated
+ * link; one spare word). Every CTA signals every rank after its stores have landed and then waits until
  * all CTAs of all ranks have signalled this rank, so when the kernel ends the whole gathered result
  * is in this rank's buffer: no collective has to follow. All ranks must make the same sequence of
  * calls on one set of (gathered, signals, state). A rank may start call i+1 on a set while a peer
