@@ -433,14 +433,14 @@ def run_ours(args, spec, rank, world, local_rank):
 # dram__bytes_write.sum) summarised under profiles/, each tagged with source_tag() of the kernel
 # source it was taken from: a figure whose tag differs from the running kernel's is stale.
 KERNEL_TRAFFIC = {
-    "sharded": dict(read=677.6e6, write=1108.0e6, source="a3f1c224d168", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
-    "prefill_gate_up": dict(read=199.5e6, write=248.1e6, source="a3f1c224d168", profile="profiles/gemm_i8_kernel_prefill_gate_up.md"),
-    "prefill_down": dict(read=379.8e6, write=32.1e6, source="a3f1c224d168", profile="profiles/gemm_i8_kernel_prefill_down.md"),
+    "sharded": dict(read=651.2e6, write=1104.0e6, source="0f2832dcfebf", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
+    "prefill_gate_up": dict(read=199.5e6, write=246.7e6, source="0f2832dcfebf", profile="profiles/gemm_i8_kernel_prefill_gate_up.md"),
+    "prefill_down": dict(read=381.1e6, write=32.9e6, source="0f2832dcfebf", profile="profiles/gemm_i8_kernel_prefill_down.md"),
     # one rank's channel shard of the sharded workload, captured on one GPU (--shard-of G): its own reads and the
     # writes of its own block; run_ours adds the peers' blocks that arrive over NVLink
-    "sharded/2": dict(read=372.0e6, write=535.1e6, source="a3f1c224d168", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
-    "sharded/4": dict(read=226.3e6, write=249.4e6, source="a3f1c224d168", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
-    "sharded/8": dict(read=152.3e6, write=105.0e6, source="a3f1c224d168", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
+    "sharded/2": dict(read=368.9e6, write=532.6e6, source="0f2832dcfebf", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
+    "sharded/4": dict(read=227.2e6, write=248.3e6, source="0f2832dcfebf", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
+    "sharded/8": dict(read=152.7e6, write=104.9e6, source="0f2832dcfebf", profile="profiles/gemm_i8_kernel_sharded_traffic.md"),
 }
 
 
