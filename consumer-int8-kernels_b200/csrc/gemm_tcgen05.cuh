@@ -116,7 +116,7 @@ __device__ __forceinline__ void grouped_item(const GemmParams& p, int item, int&
 // d's GPU, one per source rank; signal[0] is this GPU's own set. Every CTA of rank `source` adds one
 // to counter `source` of every destination after its tile stores have completed, then waits until
 // each of its own GPU's counters shows that all CTAs of that rank have arrived for this call: when the
-// kernel ends, the whole gathered result is in this GPU's memory. state (two 64-bit words in this
+// kernel ends, the whole gathered result is in this GPU's memory. state (four 64-bit words in this
 // GPU's memory, zero at first) counts the calls, so that a call can be replayed from a CUDA graph:
 // state[0] = completed calls, state[1] = CTAs of the running call that have left, state[2] = tiles drawn in
 // the running call (see kDrawSlots), zero between calls; state[3] is spare.
